@@ -9,11 +9,14 @@ import torch
 
 @dataclass(frozen=True)
 class KVRequirement:
-    """Keys and values of every position (window None) or of the last ``window`` positions."""
+    """Keys and values of every position (window None) or of the last ``window`` positions.
+    ``shared_values``: one tensor serves as both (a layer that caches a single vector a token, from
+    which it derives keys and values); ``view.v`` is then ``view.k``."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    shared_values: bool = False
 
 
 @dataclass(frozen=True)

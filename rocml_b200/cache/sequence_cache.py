@@ -45,7 +45,7 @@ class KVGroup:
         self.max_pages_per_seq = max_pages_per_seq
         shape = (n_entries, n_pages, req.n_kv_heads, PAGE, req.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = self.k if req.shared_values else torch.zeros(shape, dtype=dtype, device=device)
         self.pool = FreeList(n_pages, "page")
         self.table_host = np.full((max_slots, max_pages_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
@@ -60,7 +60,7 @@ class KVGroup:
         return self.req.window
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (1 if self.req.shared_values else 2) * self.k.numel() * self.k.element_size()
 
     def ensure(self, slot: int, new_len: int, old_len: int = 0) -> None:
         """Pages for positions < new_len (those a window has released stay released).  ``old_len``: the

@@ -36,11 +36,21 @@ def registered_architectures():
     return tuple(sorted(_ARCHITECTURES))
 
 
-def config_from_dict(d: dict):
+def architecture_name(d: dict) -> str:
+    """The architecture a config.json names: the first of ``architectures`` (Hugging Face's list), else the
+    string ``architecture``."""
     archs = d.get("architectures") or []
+    if isinstance(archs, str):
+        archs = [archs]
+    if not archs and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]
     if not archs:
-        raise ConfigError("config.json lacks 'architectures'")
-    name = archs[0]
+        raise ConfigError("config.json lacks 'architectures' (a list) and 'architecture' (a name)")
+    return archs[0]
+
+
+def config_from_dict(d: dict):
+    name = architecture_name(d)
     if name not in _ARCHITECTURES:
         raise UnsupportedArchitecture(name, registered_architectures())
     return _ARCHITECTURES[name](d)
@@ -101,7 +111,7 @@ class CatalogEntry:
 
     @property
     def architecture(self) -> str:
-        return self.config["architectures"][0]
+        return architecture_name(self.config)
 
 
 @dataclass(frozen=True)

@@ -45,6 +45,8 @@ class PositionSpec:
 
     kind "rope_neox": rotate-half rotary embedding over the first ``rot_dim``
     dimensions of every head with base ``theta``; kind "none": nothing.
+    As a model's ``input_position`` (added to the embedding output, not applied inside a mixer):
+    kind "sinusoid": entry 2i of the vector is sin(pos * theta^(-2i / width)), entry 2i + 1 the cosine.
     """
 
     kind: str = "rope_neox"
@@ -74,6 +76,10 @@ class MixerSpec:
     params_items: Tuple[Tuple[str, Any], ...] = ()
     position: PositionSpec = PositionSpec(kind="none")
 
+    # Kind "latent_attention" (keys and values unfolded from one cached latent vector a token): n_heads, head_dim
+    # (queries and keys), v_head_dim, kv_rank, latent_norm_eps, window, scale, gated (a sigmoid gate per head on the
+    # attention's output, read from the mixer's input), names (roles q, down, latent_norm, up_k, up_v, gate, o).
+
     @staticmethod
     def make(kind: str, position: Optional[PositionSpec] = None, **params) -> "MixerSpec":
         return MixerSpec(kind, _frozen_params(params), position or PositionSpec(kind="none"))
@@ -90,6 +96,11 @@ class FeedForwardSpec:
     gated_mlp params: intermediate, activation ("silu"), bias, names (the
     tensor-name stems under the layer's feed-forward prefix, by role: gate,
     up, down; default gate_proj, up_proj, down_proj).
+
+    routed_mlp (a router and ``experts`` small gated feed-forwards, ``top`` of them a token) params: experts, top,
+    intermediate, activation ("silu" or "clamped_swish" with ``limit`` and ``alpha``), score ("sigmoid"),
+    choice_bias (a per-expert vector added to the scores for the choice only), renormalize, names (roles router,
+    choice_bias, expert (a pattern with {e}), gate, up, down).
     """
 
     kind: str
@@ -109,6 +120,8 @@ class LayerSpec:
     """One layer: two norms, a mixer and a feed-forward in a named arrangement.
 
     arrangement "pre_norm": x += mixer(norm1(x)); x += ff(norm2(x)).
+    arrangement "sandwich_norm": x += post1(mixer(norm1(x))); x += post2(ff(norm2(x))), with the two
+    post norms given by ``mixer_post_norm`` and ``ff_post_norm``; ``feed_forward`` None leaves the second half out.
     ``prefix`` is the layer's tensor-name prefix in the weight files; under it the four parts'
     tensors are named ``<prefix>.<mixer_norm_name>.weight``, ``<prefix>.<mixer_name><stem>...``,
     ``<prefix>.<ff_norm_name>.weight`` and ``<prefix>.<ff_name><stem>...`` (the defaults are the
@@ -117,7 +130,7 @@ class LayerSpec:
 
     prefix: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
     ff_norm: NormSpec
     arrangement: str = "pre_norm"
@@ -125,6 +138,10 @@ class LayerSpec:
     mixer_name: str = "self_attn."
     ff_norm_name: str = "post_attention_layernorm"
     ff_name: str = "mlp."
+    mixer_post_norm: Optional[NormSpec] = None
+    ff_post_norm: Optional[NormSpec] = None
+    mixer_post_norm_name: str = "post_mixer_norm"
+    ff_post_norm_name: str = "post_ff_norm"
 
 
 @dataclass(frozen=True)
@@ -132,11 +149,18 @@ class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes ``ModelSpec.layers``.
 
     ``reads_cache_of`` names an earlier schedule entry whose cache this run
-    reads instead of keeping its own (it then writes nothing).
+    reads instead of keeping its own (it then writes nothing).  Every other
+    entry keeps a cache of its own, also when its layer runs more than once.
+
+    Before the run, two things may be added to the residual stream, in this
+    order: the embedding output (``add_input``), and row ``add_row[1]`` of the
+    [``add_row[2]``, hidden] tensor named ``add_row[0]``.
     """
 
     layer: int
     reads_cache_of: Optional[int] = None
+    add_input: bool = False
+    add_row: Optional[Tuple[str, int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -156,6 +180,10 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     stop_tokens: Tuple[int, ...] = ()
     extra: Tuple[Tuple[str, Any], ...] = field(default=())
+    embedding_scale: float = 1.0                       # the gathered rows are multiplied by it
+    input_position: Optional[PositionSpec] = None      # a position vector added to the embedding output
+    logit_scale: float = 1.0                           # the head's result is multiplied by it
+    weight_suffix: str = ".weight"                     # what the files append to a part's tensor-name stem
 
     def __post_init__(self):
         n = len(self.layers)

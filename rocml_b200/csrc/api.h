@@ -16,6 +16,48 @@ int rb_add_rmsnorm(float* resid, const float* delta, int n_delta, long long delt
 int rb_silu_mul(const void* in, int in_dtype, int n_in, long long in_stride, void* out, int out_dtype, int rows,
                 int I, int paired, void* stream);
 
+// Embedding rows times `scale` plus, when inv_freq is given, a sinusoid position vector (even entries sine, odd
+// cosine of positions[t] * inv_freq[i / 2]); `copy` (optional) receives the same rows.
+int rb_embedding_pos(const int* ids, const void* table, int table_dtype, float* out, float* copy, int T, int H,
+                     int vocab, float scale, const int* positions, const float* inv_freq, int* status, void* stream);
+
+// resid += sum of delta partial sums (+ other) (+ vec, broadcast over the rows); each may be absent.
+int rb_residual_inject(float* resid, const float* delta, int n_delta, long long delta_stride, const float* other,
+                       const void* vec, int vec_dtype, int T, int H, void* stream);
+
+// resid += rmsnorm(sum of delta) * w_post; out = rmsnorm(resid) * w_next when w_next is given.
+int rb_postnorm_add_norm(float* resid, const float* delta, int n_delta, long long delta_stride, const void* w_post,
+                         float eps_post, const void* w_next, float eps_next, int w_dtype, void* out, int out_dtype,
+                         int n_rows, int H, void* stream);
+
+// [gate | up] halves -> out; kind 0: silu(g) * u; kind 1: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u) + 1).
+int rb_gated_act(const void* in, int in_dtype, int n_in, long long in_stride, long long in_ld, void* out, int out_dtype,
+                 long long out_ld, int rows, int I, int kind, float limit, float alpha, void* stream);
+
+int rb_scale(float* x, long long n, float factor, void* stream);
+
+// A latent-attention layer's projection rows [queries | latent | gate logits]: latent normalised into the paged
+// cache, queries (when q_out is given) and sigmoid(gates) written out (latent.cu).
+int rb_latent_prep(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_width, int rank,
+                   int n_gate, const void* w, int w_dtype, float eps, void* q_out, int q_stride, float* gate_out,
+                   void* cache, int act_dtype, const int* positions, const int* slot_of_token, const int* block_table,
+                   int max_pages, int T, void* stream);
+
+// Routed experts (routing.cu).
+int rb_moe_route(const float* z, int ldz, const void* bias, int bias_dtype, const int* slot_of_token, int T, int E,
+                 int top, int* ids, float* weights, int* place, int* counts, void* stream);
+int rb_moe_plan(const int* counts, int E, int tile_rows, int max_tiles, int* starts, int* tile_group, void* stream);
+int rb_moe_gather(const void* x, int dtype, int H, const int* ids, const int* place, const int* starts, int T, int top,
+                  void* rows, int* row_of, void* stream);
+int rb_moe_combine(const float* y, long long ldy, const int* row_of, const float* weights, int T, int top, float* out,
+                   int H, void* stream);
+
+// Many small products in one launch, by head or by tiles of sorted rows (grouped_matmul.cu).
+int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int x_col_stride, const void* w, int w_dtype,
+                      long long w_group_stride, void* out, int out_dtype, long long ldo, int o_col_stride, int M, int N,
+                      int K, int groups, const int* tile_group, int tile_rows, const float* row_scale, int row_scale_ld,
+                      void* stream);
+
 // Keeps the stream busy for about that long (at most a second): the profiler's gate.
 int rb_hold(long long microseconds, void* stream);
 int rb_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* stream);

@@ -370,3 +370,236 @@ extern "C" int rb_cast(const void* in, int in_dtype, void* out, int out_dtype, l
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
+
+// ---- embedding with a multiplier and an added sinusoid position vector ----------------------------
+// out[t, i] = f32(table[ids[t], i]) * scale + (i even ? sin : cos)(positions[t] * inv_freq[i / 2]);
+// inv_freq (float32 [ceil(H / 2)]) may be absent: then nothing is added.  `copy` (optional) receives the
+// same rows (a model that adds its embedding output back in later keeps them).  Angle, sine and cosine
+// are 32-bit and full precision.
+template <typename WT>
+__global__ void embedding_pos_kernel(const int* __restrict__ ids, const WT* __restrict__ table, float* __restrict__ out,
+                                     float* __restrict__ copy, int H, int vocab, float scale,
+                                     const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                     int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool bad = id < 0 || id >= vocab;
+    if (bad && threadIdx.x == 0 && status) atomicExch(status, RB_ERR_BAD_SIZE);
+    const WT* row = table + (size_t)(bad ? 0 : id) * H;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = bad ? 0.f : to_f32(row[i]) * scale;
+        if (inv_freq) {
+            const float a = pos * inv_freq[i >> 1];
+            v += (i & 1) ? cosf(a) : sinf(a);
+        }
+        out[(size_t)t * H + i] = v;
+        if (copy) copy[(size_t)t * H + i] = v;
+    }
+}
+
+extern "C" int rb_embedding_pos(const int* ids, const void* table, int table_dtype, float* out, float* copy, int T,
+                                int H, int vocab, float scale, const int* positions, const float* inv_freq,
+                                int* status, void* stream) {
+    if (T <= 0) return RB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == RB_BF16)
+        RB_LAUNCH((embedding_pos_kernel<__nv_bfloat16>), dim3(T), dim3(threads), 0, s, ids, (const __nv_bfloat16*)table, out,
+                  copy, H, vocab, scale, positions, inv_freq, status);
+    else if (table_dtype == RB_F32)
+        RB_LAUNCH((embedding_pos_kernel<float>), dim3(T), dim3(threads), 0, s, ids, (const float*)table, out, copy, H, vocab,
+                  scale, positions, inv_freq, status);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// ---- additions into the residual stream between layers -----------------------------------------------
+// resid[t, :] = ((resid[t, :] + sum_s delta[s][t, :]) + other[t, :]) + vec[:]; each of delta, other, vec may
+// be absent.  The additions are 32-bit and in this order for every element.
+template <typename WT>
+__global__ void residual_inject_kernel(float* __restrict__ resid, const float* __restrict__ delta, int n_delta,
+                                       size_t delta_stride, const float* __restrict__ other, const WT* __restrict__ vec,
+                                       size_t n, int H) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = resid[i];
+        for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + i];
+        if (other) v += other[i];
+        if (vec) v += to_f32(vec[i % H]);
+        resid[i] = v;
+    }
+}
+
+extern "C" int rb_residual_inject(float* resid, const float* delta, int n_delta, long long delta_stride,
+                                  const float* other, const void* vec, int vec_dtype, int T, int H, void* stream) {
+    if (T <= 0) return RB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = (size_t)T * H;
+    const int threads = 256;
+    const size_t want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (vec_dtype == RB_BF16)
+        RB_LAUNCH((residual_inject_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, s, resid, delta, n_delta,
+                  (size_t)delta_stride, other, (const __nv_bfloat16*)vec, n, H);
+    else if (vec_dtype == RB_F32)
+        RB_LAUNCH((residual_inject_kernel<float>), dim3(blocks), dim3(threads), 0, s, resid, delta, n_delta,
+                  (size_t)delta_stride, other, (const float*)vec, n, H);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// ---- a norm on a sublayer's output, the addition, and the next sublayer's norm --------------------------
+// d = sum_s delta[s][row]  (s in order);  resid[row] += d * rsqrt(mean(d^2) + eps_post) * w_post;
+// if w_next: out[row] = resid[row] * rsqrt(mean(resid[row]^2) + eps_next) * w_next.
+// One block a row; the row stays in shared memory between the passes.  All arithmetic is 32-bit.
+template <typename OT, typename WT>
+__global__ void __launch_bounds__(1024) postnorm_add_norm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
+                                                                 int n_delta, size_t delta_stride,
+                                                                 const WT* __restrict__ w_post, float eps_post,
+                                                                 const WT* __restrict__ w_next, float eps_next,
+                                                                 OT* __restrict__ out, int H) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float row_buf[];  // H floats (padded to 4) + 33 for the reductions
+    float* red = row_buf + ((H + 3) & ~3);
+    const int row = blockIdx.x;
+    float* r = resid + (size_t)row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + (size_t)row * H + i];
+        row_buf[i] = v;
+        ss += v * v;
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps_post);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = r[i] + row_buf[i] * inv * to_f32(w_post[i]);
+        r[i] = v;
+        row_buf[i] = v;
+        ss2 += v * v;
+    }
+    if (!w_next) return;
+    const float inv2 = rsqrtf(block_sum(ss2, red) / (float)H + eps_next);
+    OT* o = out + (size_t)row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<OT>(row_buf[i] * inv2 * to_f32(w_next[i]));
+}
+
+template <typename OT, typename WT>
+static int launch_postnorm(float* resid, const float* delta, int n_delta, size_t delta_stride, const void* w_post,
+                           float eps_post, const void* w_next, float eps_next, void* out, int n_rows, int H,
+                           cudaStream_t s) {
+    const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
+    if (smem > 200 * 1024) return RB_ERR_BAD_SIZE;
+    auto k = postnorm_add_norm_kernel<OT, WT>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+    RB_LAUNCH((k), dim3(n_rows), dim3(threads), smem, s, resid, delta, n_delta, delta_stride, (const WT*)w_post, eps_post,
+              (const WT*)w_next, eps_next, (OT*)out, H);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_postnorm_add_norm(float* resid, const float* delta, int n_delta, long long delta_stride,
+                                    const void* w_post, float eps_post, const void* w_next, float eps_next, int w_dtype,
+                                    void* out, int out_dtype, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return RB_OK;
+    if (n_delta < 1 || !delta || !w_post) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t ds = (size_t)delta_stride;
+    if (out_dtype == RB_BF16 && w_dtype == RB_BF16)
+        return launch_postnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+    if (out_dtype == RB_BF16 && w_dtype == RB_F32)
+        return launch_postnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+    if (out_dtype == RB_F32 && w_dtype == RB_BF16)
+        return launch_postnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+    if (out_dtype == RB_F32 && w_dtype == RB_F32)
+        return launch_postnorm<float, float>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+    return RB_ERR_BAD_DTYPE;
+}
+
+// ---- gated activations on a stacked [gate | up] product ------------------------------------------------
+// in: [S][rows, 2 * I] (S partial sums, added first, in order), gates in columns 0 .. I - 1 and ups in
+// I .. 2 I - 1; out: [rows, I].
+//   kind 0: silu(g) * u, silu(g) = g / (1 + exp(-g))
+//   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(alpha * g') * (u' + 1)
+template <typename IT, typename OT>
+__global__ void gated_act_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, size_t in_ld, OT* __restrict__ out,
+                                 size_t out_ld, int rows, int I, int kind, float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t n = (size_t)rows * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < n_in; ++s) {
+            g += to_f32(in[(size_t)s * in_stride + t * in_ld + i]);
+            u += to_f32(in[(size_t)s * in_stride + t * in_ld + I + i]);
+        }
+        float v;
+        if (kind == 0) {
+            v = g / (1.f + expf(-g)) * u;
+        } else {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+            v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+        }
+        out[t * out_ld + i] = from_f32<OT>(v);
+    }
+}
+
+extern "C" int rb_gated_act(const void* in, int in_dtype, int n_in, long long in_stride, long long in_ld, void* out,
+                            int out_dtype, long long out_ld, int rows, int I, int kind, float limit, float alpha,
+                            void* stream) {
+    if (rows <= 0 || I <= 0) return RB_OK;
+    if (n_in < 1 || kind < 0 || kind > 1) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = (size_t)rows * I;
+    const int threads = 256;
+    const size_t want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    typedef __nv_bfloat16 bf;
+    if (in_dtype == RB_BF16 && out_dtype == RB_BF16)
+        RB_LAUNCH((gated_act_kernel<bf, bf>), dim3(blocks), dim3(threads), 0, s, (const bf*)in, n_in, (size_t)in_stride,
+                  (size_t)in_ld, (bf*)out, (size_t)out_ld, rows, I, kind, limit, alpha);
+    else if (in_dtype == RB_F32 && out_dtype == RB_BF16)
+        RB_LAUNCH((gated_act_kernel<float, bf>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride,
+                  (size_t)in_ld, (bf*)out, (size_t)out_ld, rows, I, kind, limit, alpha);
+    else if (in_dtype == RB_F32 && out_dtype == RB_F32)
+        RB_LAUNCH((gated_act_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride,
+                  (size_t)in_ld, (float*)out, (size_t)out_ld, rows, I, kind, limit, alpha);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// ---- x *= factor (32-bit, in place) ----------------------------------------------------------------------
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float factor) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] *= factor;
+}
+
+extern "C" int rb_scale(float* x, long long n, float factor, void* stream) {
+    if (n <= 0) return RB_OK;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    RB_LAUNCH((scale_kernel), dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, x, (size_t)n, factor);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}

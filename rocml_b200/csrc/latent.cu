@@ -1,0 +1,94 @@
+// What stands between a latent-attention layer's input projection and its attention.
+//
+// The projection's rows are [queries (q_width) | latent (rank) | gate logits (n_gate)], as the matrix
+// product left them: S partial sums of 32-bit rows, or one row in the activations' type.  For every
+// token of the step, one block
+//   * adds the partial sums,
+//   * normalises the latent: c = x * rsqrt(mean(x^2) + eps) * w (32-bit), and writes it to the token's
+//     place in the paged cache ([pages][1][64][rank], the layer's only cached tensor),
+//   * writes the queries in the activations' type when they arrived as partial sums (q_out absent: they
+//     stay where they are),
+//   * writes sigmoid(gate logit) per head in 32-bit.
+// Padding tokens (slot -1) are skipped.
+#include "common.cuh"
+#include "api.h"
+
+using namespace rb;
+
+namespace {
+template <typename IT, typename AT, typename WT>
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int q_width, int rank, int n_gate,
+                   const WT* __restrict__ w, float eps, AT* __restrict__ q_out, int q_stride, float* __restrict__ gate_out,
+                   AT* __restrict__ cache, const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                   const int* __restrict__ block_table, int max_pages) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float buf[];          // rank floats + 33
+    float* red = buf + rank;
+    const int t = blockIdx.x;
+    const int slot = slot_of_token[t];
+    if (slot < 0) return;
+    const IT* row = in + (size_t)t * row_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_in; ++s) v += to_f32(row[(size_t)s * in_stride + q_width + i]);
+        buf[i] = v;
+        ss += v * v;
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / (float)rank + eps);
+    const int pos = positions[t];
+    const int page = block_table[(size_t)slot * max_pages + pos / RB_PAGE];
+    if (page >= 0) {
+        AT* dst = cache + ((size_t)page * RB_PAGE + (pos % RB_PAGE)) * rank;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f32<AT>(buf[i] * inv * to_f32(w[i]));
+    }
+    if (q_out) {
+        for (int i = threadIdx.x; i < q_width; i += blockDim.x) {
+            float v = 0.f;
+            for (int s = 0; s < n_in; ++s) v += to_f32(row[(size_t)s * in_stride + i]);
+            q_out[(size_t)t * q_stride + i] = from_f32<AT>(v);
+        }
+    }
+    for (int i = threadIdx.x; i < n_gate; i += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_in; ++s) v += to_f32(row[(size_t)s * in_stride + q_width + rank + i]);
+        gate_out[(size_t)t * n_gate + i] = 1.f / (1.f + expf(-v));
+    }
+}
+
+template <typename IT, typename AT, typename WT>
+int launch_prep(const void* in, int n_in, long long in_stride, int row_stride, int q_width, int rank, int n_gate,
+                const void* w, float eps, void* q_out, int q_stride, float* gate_out, void* cache, const int* positions,
+                const int* slot_of_token, const int* block_table, int max_pages, int T, cudaStream_t s) {
+    const size_t smem = (size_t)(rank + 33) * sizeof(float);
+    if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
+    RB_LAUNCH((latent_prep_kernel<IT, AT, WT>), dim3(T), dim3(128), smem, s, (const IT*)in, n_in, (size_t)in_stride, row_stride,
+              q_width, rank, n_gate, (const WT*)w, eps, (AT*)q_out, q_stride, gate_out, (AT*)cache, positions, slot_of_token,
+              block_table, max_pages);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+}  // namespace
+
+extern "C" int rb_latent_prep(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_width,
+                              int rank, int n_gate, const void* w, int w_dtype, float eps, void* q_out, int q_stride,
+                              float* gate_out, void* cache, int act_dtype, const int* positions, const int* slot_of_token,
+                              const int* block_table, int max_pages, int T, void* stream) {
+    if (T <= 0) return RB_OK;
+    if (rank <= 0 || n_in < 1 || (n_gate > 0 && !gate_out)) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+#define RB_LP(IT, AT, WT) return launch_prep<IT, AT, WT>(in, n_in, in_stride, row_stride, q_width, rank, n_gate, w, eps, q_out, \
+                                                        q_stride, gate_out, cache, positions, slot_of_token, block_table,   \
+                                                        max_pages, T, s)
+    if (in_dtype == RB_F32 && act_dtype == RB_BF16 && w_dtype == RB_BF16) RB_LP(float, bf, bf);
+    if (in_dtype == RB_F32 && act_dtype == RB_BF16 && w_dtype == RB_F32) RB_LP(float, bf, float);
+    if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_BF16) RB_LP(bf, bf, bf);
+    if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_F32) RB_LP(bf, bf, float);
+    if (in_dtype == RB_F32 && act_dtype == RB_F32 && w_dtype == RB_F32) RB_LP(float, float, float);
+    if (in_dtype == RB_F32 && act_dtype == RB_F32 && w_dtype == RB_BF16) RB_LP(float, float, bf);
+#undef RB_LP
+    return RB_ERR_BAD_DTYPE;
+}

@@ -1,0 +1,183 @@
+// Routing of tokens to experts: scores and choice, the plan of rows, the gather and the weighted sum.
+//
+//   route    one warp a token: s_e = sigmoid(z_e) (z: 32-bit router logits); the `top` experts with the
+//            largest s_e + bias_e are chosen (ties: the lower number), their weights are s_e (without the
+//            bias, not renormalised).  Each choice also takes the next free place among its expert's rows
+//            (an atomic counter: the order of an expert's rows is arbitrary, and no result depends on it,
+//            because every row is computed by itself).  Padding tokens (slot -1) choose nothing.
+//   plan     one block: every expert's rows start at a multiple of `tile_rows`; tile i of the row buffer
+//            belongs to expert tile_group[i] (-1: unused).
+//   gather   a token's normalised row is copied to each of its `top` places; row_of[t, j] names the place.
+//   combine  out[t] = sum_j weight[t, j] * y[row_of[t, j]] in 32-bit, j ascending.
+#include "common.cuh"
+#include "api.h"
+
+using namespace rb;
+
+namespace {
+constexpr int MAX_EPL = 16;   // experts per lane: up to 512 experts
+
+template <typename BT>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ z, int ldz, const BT* __restrict__ bias, const int* __restrict__ slot_of_token,
+                 int T, int E, int top, int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ place,
+                 int* __restrict__ counts) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= T) return;
+    if (slot_of_token[t] < 0) {
+        for (int j = lane; j < top; j += 32) { ids[(size_t)t * top + j] = -1; weights[(size_t)t * top + j] = 0.f; place[(size_t)t * top + j] = 0; }
+        return;
+    }
+    float s[MAX_EPL], c[MAX_EPL];
+#pragma unroll
+    for (int i = 0; i < MAX_EPL; ++i) {
+        const int e = lane + i * 32;
+        if (e < E) {
+            s[i] = 1.f / (1.f + expf(-z[(size_t)t * ldz + e]));
+            c[i] = s[i] + (bias ? to_f32(bias[e]) : 0.f);
+        } else {
+            s[i] = 0.f;
+            c[i] = -INFINITY;
+        }
+    }
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY, best_s = 0.f;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < MAX_EPL; ++i) {
+            const int e = lane + i * 32;
+            if (e < E && (c[i] > best)) { best = c[i]; best_e = e; best_s = s[i]; }   // ascending e: the first of equals stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_s = os; }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_EPL; ++i)
+            if (lane + i * 32 == best_e) c[i] = -INFINITY;
+        if (best_e >= E) best_e = E - 1;      // scores that compare with nothing (NaN): stay inside the tables
+        if (lane == 0) {
+            ids[(size_t)t * top + j] = best_e;
+            weights[(size_t)t * top + j] = best_s;
+            place[(size_t)t * top + j] = atomicAdd(&counts[best_e], 1);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_plan_kernel(const int* __restrict__ counts, int E, int tile_rows, int max_tiles, int* __restrict__ starts,
+                int* __restrict__ tile_group) {
+    pdl_trigger();
+    pdl_wait();
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_group[i] = -1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < E; ++e) {
+            starts[e] = tile * tile_rows;
+            const int n = (counts[e] + tile_rows - 1) / tile_rows;
+            for (int i = 0; i < n && tile + i < max_tiles; ++i) tile_group[tile + i] = e;
+            tile += n;
+        }
+        starts[E] = tile * tile_rows;
+    }
+}
+
+template <typename AT>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const AT* __restrict__ x, int H, const int* __restrict__ ids, const int* __restrict__ place,
+                  const int* __restrict__ starts, int top, AT* __restrict__ rows, int* __restrict__ row_of) {
+    pdl_trigger();
+    pdl_wait();
+    const int tj = blockIdx.x;
+    const int e = ids[tj];
+    if (e < 0) {
+        if (threadIdx.x == 0) row_of[tj] = -1;
+        return;
+    }
+    const int r = starts[e] + place[tj];
+    if (threadIdx.x == 0) row_of[tj] = r;
+    const AT* src = x + (size_t)(tj / top) * H;
+    AT* dst = rows + (size_t)r * H;
+    if ((H * sizeof(AT)) % 16 == 0 && (((uintptr_t)x | (uintptr_t)rows) & 15) == 0) {
+        const int n16 = (int)(H * sizeof(AT) / 16);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, long long ldy, const int* __restrict__ row_of, const float* __restrict__ weights,
+                   int top, float* __restrict__ out, int H) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int r = row_of[(size_t)t * top + j];
+            if (r >= 0) v = fmaf(weights[(size_t)t * top + j], y[(size_t)r * ldy + i], v);
+        }
+        out[(size_t)t * H + i] = v;
+    }
+}
+}  // namespace
+
+extern "C" int rb_moe_route(const float* z, int ldz, const void* bias, int bias_dtype, const int* slot_of_token, int T,
+                            int E, int top, int* ids, float* weights, int* place, int* counts, void* stream) {
+    if (T <= 0) return RB_OK;
+    if (E <= 0 || E > 32 * MAX_EPL || top <= 0 || top > E) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int warps = 4;
+    dim3 grid((T + warps - 1) / warps);
+    if (!bias || bias_dtype == RB_F32)
+        RB_LAUNCH((moe_route_kernel<float>), grid, dim3(warps * 32), 0, s, z, ldz, (const float*)bias, slot_of_token, T, E, top,
+                  ids, weights, place, counts);
+    else if (bias_dtype == RB_BF16)
+        RB_LAUNCH((moe_route_kernel<__nv_bfloat16>), grid, dim3(warps * 32), 0, s, z, ldz, (const __nv_bfloat16*)bias,
+                  slot_of_token, T, E, top, ids, weights, place, counts);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_moe_plan(const int* counts, int E, int tile_rows, int max_tiles, int* starts, int* tile_group,
+                           void* stream) {
+    if (E <= 0 || tile_rows <= 0 || max_tiles <= 0) return RB_ERR_BAD_SIZE;
+    RB_LAUNCH((moe_plan_kernel), dim3(1), dim3(256), 0, (cudaStream_t)stream, counts, E, tile_rows, max_tiles, starts, tile_group);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_moe_gather(const void* x, int dtype, int H, const int* ids, const int* place, const int* starts, int T,
+                             int top, void* rows, int* row_of, void* stream) {
+    if (T <= 0) return RB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RB_BF16)
+        RB_LAUNCH((moe_gather_kernel<__nv_bfloat16>), dim3(T * top), dim3(128), 0, s, (const __nv_bfloat16*)x, H, ids, place,
+                  starts, top, (__nv_bfloat16*)rows, row_of);
+    else if (dtype == RB_F32)
+        RB_LAUNCH((moe_gather_kernel<float>), dim3(T * top), dim3(128), 0, s, (const float*)x, H, ids, place, starts, top,
+                  (float*)rows, row_of);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+extern "C" int rb_moe_combine(const float* y, long long ldy, const int* row_of, const float* weights, int T, int top,
+                              float* out, int H, void* stream) {
+    if (T <= 0) return RB_OK;
+    RB_LAUNCH((moe_combine_kernel), dim3(T), dim3(256), 0, (cudaStream_t)stream, y, ldy, row_of, weights, top, out, H);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}

@@ -101,7 +101,7 @@ class Engine:
             if src is not None or r is None:
                 continue
             if hasattr(r, "n_kv_heads"):
-                per_token += 2 * r.n_kv_heads * r.head_dim * esz
+                per_token += (1 if getattr(r, "shared_values", False) else 2) * r.n_kv_heads * r.head_dim * esz
             elif hasattr(r, "shape"):
                 n = 1
                 for d in r.shape:
@@ -393,5 +393,5 @@ class Engine:
         (rocml/src/budget/mod.rs:47-59: 2 * layers * kv heads * head size * element size)."""
         n = 0
         for g in self.cache.kv_groups:
-            n += 2 * g.n_entries * g.req.n_kv_heads * g.req.head_dim * g.k.element_size()
+            n += (1 if g.req.shared_values else 2) * g.n_entries * g.req.n_kv_heads * g.req.head_dim * g.k.element_size()
         return n

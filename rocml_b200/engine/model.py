@@ -15,7 +15,7 @@ from .. import kernels
 from ..profile import scope
 from ..config.specs import MixerSpec, ModelSpec
 from ..errors import ConfigError
-from ..parts import BuildEnv, build_block, build_norm
+from ..parts import BuildEnv, build_block, build_norm, build_position
 from ..parts.linear import Linear
 from ..weights.decl import TensorDecl
 from ..weights.loader import load_tensors
@@ -42,10 +42,36 @@ class Model:
         self.head = Linear([spec.head_name[: -len(".weight")]], [spec.vocab], spec.hidden, False, env)
         self.embed: Optional[torch.Tensor] = None
         self.status: Optional[torch.Tensor] = None
+        # a position vector added to the embedding output (its table of frequencies lives on the device)
+        self.input_position = None
+        if spec.input_position is not None and spec.input_position.kind != "none":
+            self.input_position = build_position(spec.input_position, spec.hidden, env)
+            if getattr(self.input_position, "width", None) != spec.hidden:
+                raise ConfigError(f"position encoding {spec.input_position.kind!r} cannot be added to the embedding output")
+        # tensors whose rows are added to the residual stream before some runs: name -> rows
+        self.added_rows: Dict[str, int] = {}
+        for e in spec.schedule:
+            if e.add_row is not None:
+                name, row, rows = e.add_row
+                if not 0 <= row < rows or self.added_rows.setdefault(name, rows) != rows:
+                    raise ConfigError(f"schedule: row {row} of {name!r} ({rows} rows) does not fit")
+        self.added: Dict[str, torch.Tensor] = {}
+        self.keeps_input = any(e.add_input for e in spec.schedule)
 
     # ---- tensors ------------------------------------------------------------------------------
-    def declare(self) -> List[TensorDecl]:
+    # Parts name their tensors '<stem>.weight'; the files of an architecture may append something else to
+    # the stem, or nothing (``ModelSpec.weight_suffix``).  ``declare`` speaks the files' names, ``load``
+    # takes them and hands the parts theirs.
+    def _file_name(self, name: str) -> str:
+        suffix = self.spec.weight_suffix
+        if suffix != ".weight" and name.endswith(".weight"):
+            return name[: -len(".weight")] + suffix
+        return name
+
+    def _declare_parts(self) -> List[TensorDecl]:
         out = [TensorDecl(self.spec.embedding_name, (self.vocab, self.hidden), "matrix")]
+        for name, rows in self.added_rows.items():
+            out.append(TensorDecl(name, (rows, self.hidden), "matrix"))
         for b in self.blocks:
             out += b.declare()
         out += self.final_norm.declare(self.spec.final_norm_name[: -len(".weight")])
@@ -53,13 +79,19 @@ class Model:
             out += self.head.declare("")
         return out
 
+    def declare(self) -> List[TensorDecl]:
+        return [TensorDecl(self._file_name(d.name), d.shape, d.role) for d in self._declare_parts()]
+
     def ignorable(self) -> List[str]:
         """Tensors a folder may hold that the model does not read: a stored head when the
         head is tied to the embedding."""
-        return [self.spec.head_name] if self.spec.tie_embeddings else []
+        return [self._file_name(self.spec.head_name)] if self.spec.tie_embeddings else []
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if self.spec.weight_suffix != ".weight":
+            tensors = {d.name: tensors[self._file_name(d.name)] for d in self._declare_parts()}
         self.embed = tensors[self.spec.embedding_name]
+        self.added = {name: tensors[name] for name in self.added_rows}
         for b in self.blocks:
             b.load(tensors)
         self.final_norm.load(tensors, self.spec.final_norm_name[: -len(".weight")])
@@ -127,12 +159,25 @@ class Model:
     def forward(self, batch, cache) -> Optional[torch.Tensor]:
         T = batch.n_tokens
         resid = torch.empty((T, self.hidden), dtype=torch.float32, device=self.env.device)
+        x0 = torch.empty_like(resid) if self.keeps_input else None
         with scope(op="embedding"):
-            kernels.embedding(batch.token_ids, self.embed, resid, self.status)
+            if self.input_position is None and self.spec.embedding_scale == 1.0 and x0 is None:
+                kernels.embedding(batch.token_ids, self.embed, resid, self.status)
+            else:
+                kernels.embedding_pos(batch.token_ids, self.embed, resid, self.spec.embedding_scale, batch.positions,
+                                      self.input_position.inv_freq if self.input_position is not None else None,
+                                      copy=x0, status=self.status)
         pending = None
         sched = self.spec.schedule
         for i, e in enumerate(sched):
             block = self.blocks[e.layer]
+            if e.add_input or e.add_row is not None:
+                # what the layer before left pending joins the stream first, then the embedding output, then the row
+                with scope(layer=i, op="stream_additions"):
+                    delta = pending if isinstance(pending, torch.Tensor) else None
+                    vec = self.added[e.add_row[0]][e.add_row[1]] if e.add_row is not None else None
+                    kernels.residual_inject(resid, delta, x0 if e.add_input else None, vec)
+                pending = None
             with scope(layer=i):
                 if getattr(block, "chains", False):
                     # a block may prepare the first norm of the block that follows it
@@ -146,6 +191,9 @@ class Model:
             xn = self.final_norm.forward(resid, pending, n_rows=batch.n_want, rows=batch.want_rows, write_back=False)
         logits = torch.empty((batch.n_want, self.vocab), dtype=torch.float32, device=self.env.device)
         self.head.forward(xn, logits, batch.n_want)
+        if self.spec.logit_scale != 1.0:
+            with scope(op="logit_scale"):
+                kernels.scale_(logits, self.spec.logit_scale)
         return logits
 
 

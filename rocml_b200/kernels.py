@@ -155,6 +155,19 @@ def _lib():
         lib.rb_gemm_tcgen05_residual.argtypes = [_vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp, _ll, _vp, _i, _vp, _ll, _vp,
                                                  _ll, _i, _vp, _vp]
         lib.rb_hold.argtypes = [_ll, _vp]
+        lib.rb_embedding_pos.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp]
+        lib.rb_residual_inject.argtypes = [_vp, _vp, _i, _ll, _vp, _vp, _i, _i, _i, _vp]
+        lib.rb_postnorm_add_norm.argtypes = [_vp, _vp, _i, _ll, _vp, _f, _vp, _f, _i, _vp, _i, _i, _i, _vp]
+        lib.rb_gated_act.argtypes = [_vp, _i, _i, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _f, _f, _vp]
+        lib.rb_scale.argtypes = [_vp, _ll, _f, _vp]
+        lib.rb_latent_prep.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _vp, _i, _f, _vp, _i, _vp, _vp, _i, _vp, _vp,
+                                       _vp, _i, _i, _vp]
+        lib.rb_moe_route.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
+        lib.rb_moe_plan.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp]
+        lib.rb_moe_gather.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]
+        lib.rb_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _i, _vp]
+        lib.rb_grouped_matmul.argtypes = [_vp, _i, _ll, _i, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _vp, _i,
+                                          _vp, _i, _vp]
         lib.rb_gemm_tcgen05_set_wait.argtypes = [_ll, _i]
         lib.rb_gemm_tcgen05_set_wait.restype = None
         _sigs_done = True
@@ -821,3 +834,224 @@ def gemm_tcgen05_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor,
     _check(rc, "gemm_tcgen05_qkv_rope")
     return True
 
+
+
+# ---- embedding with a multiplier and sinusoid positions; additions between layers ------------------------------
+
+@_profiled(lambda a, facts: _cost.embedding(a["out"].shape[0], a["out"].shape[1], _esz(a["table"])))
+def embedding_pos(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float, positions: torch.Tensor,
+                  inv_freq: Optional[torch.Tensor], copy: Optional[torch.Tensor] = None,
+                  status: Optional[torch.Tensor] = None):
+    """out[t, i] = float32(table[ids[t], i]) * scale + (sin | cos)(positions[t] * inv_freq[i // 2]) for even | odd i
+    (nothing is added without ``inv_freq``); ``copy`` receives the same rows."""
+    T, H = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous() or table.shape[1] != H:
+        raise KernelError("embedding_pos: out must be contiguous float32 [T, H], table contiguous [vocab, H]")
+    if copy is not None and (copy.dtype != torch.float32 or not copy.is_contiguous() or copy.shape != out.shape):
+        raise KernelError("embedding_pos: copy must look like out")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() < (H + 1) // 2):
+        raise KernelError("embedding_pos: inv_freq must be float32 [ceil(H / 2)]")
+    rc = _lib().rb_embedding_pos(_i32(ids, "ids"), _ptr(table), dtype_code(table.dtype), _ptr(out), _ptr(copy), T, H,
+                                 table.shape[0], float(scale), _i32(positions, "positions"), _ptr(inv_freq),
+                                 _ptr(status), _stream())
+    _check(rc, "embedding_pos")
+
+
+@_profiled(lambda a, facts: (a["resid"].numel() * 4 * (2 + (a["delta"].shape[0] if a["delta"] is not None else 0)
+                                                       + (1 if a["other"] is not None else 0)), a["resid"].numel() * 3))
+def residual_inject(resid: torch.Tensor, delta: Optional[torch.Tensor] = None, other: Optional[torch.Tensor] = None,
+                    vec: Optional[torch.Tensor] = None):
+    """resid [T, H] float32 += sum of delta [S, T, H] (+ other [T, H] float32) (+ vec [H], every row)."""
+    T, H = resid.shape
+    if resid.dtype != torch.float32 or not resid.is_contiguous():
+        raise KernelError("residual_inject: resid must be contiguous float32")
+    n_delta, stride = 0, 0
+    if delta is not None:
+        if delta.dtype != torch.float32 or delta.dim() != 3 or tuple(delta.shape[1:]) != (T, H) or \
+                not delta[0].is_contiguous():
+            raise KernelError("residual_inject: delta must be float32 [S, T, H]")
+        n_delta, stride = delta.shape[0], delta.stride(0)
+    if other is not None and (other.dtype != torch.float32 or not other.is_contiguous() or other.shape != resid.shape):
+        raise KernelError("residual_inject: other must look like resid")
+    if vec is not None and (vec.numel() != H or not vec.is_contiguous()):
+        raise KernelError("residual_inject: vec must be [H]")
+    rc = _lib().rb_residual_inject(_ptr(resid), _ptr(delta), n_delta, stride, _ptr(other), _ptr(vec),
+                                   dtype_code(vec.dtype) if vec is not None else F32, T, H, _stream())
+    _check(rc, "residual_inject")
+
+
+@_profiled(lambda a, facts: _cost.add_norm(a["resid"].shape[0], a["resid"].shape[1], a["delta"].shape[0],
+                                           _esz(a["out"]) if a["out"] is not None else 0, True, _esz(a["w_post"])))
+def postnorm_add_norm(resid: torch.Tensor, delta: torch.Tensor, w_post: torch.Tensor, eps_post: float,
+                      w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0, out: Optional[torch.Tensor] = None):
+    """resid [T, H] float32 += rmsnorm(sum of delta [S, T, H] float32) * w_post; with ``w_next`` and ``out`` [T, H]:
+    out = rmsnorm(resid) * w_next (the next sublayer's input)."""
+    T, H = resid.shape
+    if resid.dtype != torch.float32 or not resid.is_contiguous():
+        raise KernelError("postnorm_add_norm: resid must be contiguous float32")
+    if delta.dtype != torch.float32 or delta.dim() != 3 or delta.shape[1] < T or delta.shape[2] != H or \
+            delta.stride(2) != 1 or delta.stride(1) != H:
+        raise KernelError("postnorm_add_norm: delta must be float32 [S, >= T, H] with dense rows")
+    if (w_next is None) != (out is None):
+        raise KernelError("postnorm_add_norm: give both the next norm's weight and its output or neither")
+    if w_post.numel() != H or (w_next is not None and (w_next.numel() != H or w_next.dtype != w_post.dtype)):
+        raise KernelError("postnorm_add_norm: the norms' weights must be [H] of one type")
+    if out is not None and (not out.is_contiguous() or out.shape[-1] != H or out.numel() < T * H):
+        raise KernelError("postnorm_add_norm: out must be contiguous [T, H]")
+    rc = _lib().rb_postnorm_add_norm(_ptr(resid), _ptr(delta), delta.shape[0], delta.stride(0), _ptr(w_post),
+                                     float(eps_post), _ptr(w_next), float(eps_next), dtype_code(w_post.dtype), _ptr(out),
+                                     dtype_code(out.dtype) if out is not None else F32, T, H, _stream())
+    _check(rc, "postnorm_add_norm")
+
+
+GATED_ACTS = {"silu": 0, "clamped_swish": 1}
+
+
+@_profiled(lambda a, facts: _cost.silu_mul(a["out"].shape[0] if a["rows"] is None else a["rows"], a["out"].shape[1],
+                                           _n_in(a["x"]), _esz(a["x"]), _esz(a["out"])))
+def gated_act(x: torch.Tensor, out: torch.Tensor, kind: str = "silu", limit: float = 0.0, alpha: float = 1.0,
+              rows: Optional[int] = None):
+    """x [R, 2I] = [gate | up] (or [S, R, 2I] partial sums, added first) -> out [R, I].  ``kind`` "silu":
+    silu(gate) * up; "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit),
+    g * sigmoid(alpha * g) * (u + 1)."""
+    if kind not in GATED_ACTS:
+        raise KernelError(f"gated_act: unknown kind {kind!r} (known: {sorted(GATED_ACTS)})")
+    n_in, in_stride, row_stride = _partials(x, "gated_act")
+    R, I2 = x.shape[-2], x.shape[-1]
+    n = R if rows is None else rows
+    if I2 % 2 or out.shape[-1] != I2 // 2 or out.stride(-1) != 1 or out.shape[0] < n or n > R:
+        raise KernelError("gated_act: shapes do not fit")
+    _check(_lib().rb_gated_act(_ptr(x), dtype_code(x.dtype), n_in, in_stride, row_stride, _ptr(out), dtype_code(out.dtype),
+                               out.stride(0), n, I2 // 2, GATED_ACTS[kind], float(limit), float(alpha), _stream()),
+           "gated_act")
+
+
+@_profiled(lambda a, facts: (a["x"].numel() * 8, a["x"].numel()))
+def scale_(x: torch.Tensor, factor: float):
+    """x *= factor in place (contiguous float32)."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_: x must be contiguous float32")
+    _check(_lib().rb_scale(_ptr(x), x.numel(), float(factor), _stream()), "scale_")
+
+
+# ---- latent attention: between the projection and the attention ---------------------------------------------------
+
+@_profiled(lambda a, facts: (a["n_tokens"] * (a["proj"].shape[-1] * _esz(a["proj"]) * _n_in(a["proj"])
+                                              + (a["q_width"] + a["rank"]) * _esz(a["cache"]) + a["n_gate"] * 4),
+                             a["n_tokens"] * (a["rank"] * 6 + a["n_gate"] * 8)))
+def latent_prep(proj: torch.Tensor, n_tokens: int, q_width: int, rank: int, n_gate: int, norm_w: torch.Tensor, eps: float,
+                q_out: Optional[torch.Tensor], gate_out: Optional[torch.Tensor], cache: torch.Tensor,
+                positions: torch.Tensor, slot_of_token: torch.Tensor, block_table: torch.Tensor):
+    """proj [T, >= q_width + rank + n_gate] (or [S, T, ...] float32 partial sums) = [queries | latent | gate logits].
+    The latent is RMS-normalised (32-bit) with ``norm_w`` and written to each token's place in ``cache``
+    [pages, 1, 64, rank]; the queries go to ``q_out`` [T, q_width] in the cache's type when given; sigmoid of the
+    gate logits to ``gate_out`` float32 [T, n_gate]."""
+    n_in, in_stride, row_stride = _partials(proj, "latent_prep")
+    if proj.shape[-1] < q_width + rank + n_gate:
+        raise KernelError("latent_prep: projection rows are too narrow")
+    if tuple(cache.shape[1:]) != (1, PAGE, rank) or not cache.is_contiguous():
+        raise KernelError("latent_prep: cache must be [pages, 1, 64, rank]")
+    if norm_w.numel() != rank:
+        raise KernelError("latent_prep: the latent norm's weight must be [rank]")
+    if q_out is not None and (q_out.dtype != cache.dtype or q_out.stride(-1) != 1 or q_out.shape[-1] < q_width):
+        raise KernelError("latent_prep: q_out must hold q_width elements a row in the cache's type")
+    if n_gate and (gate_out is None or gate_out.dtype != torch.float32 or not gate_out.is_contiguous()
+                   or gate_out.shape[-1] != n_gate):
+        raise KernelError("latent_prep: gate_out must be contiguous float32 [T, n_gate]")
+    rc = _lib().rb_latent_prep(
+        _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, q_width, rank, n_gate, _ptr(norm_w),
+        dtype_code(norm_w.dtype), float(eps), _ptr(q_out), q_out.stride(0) if q_out is not None else 0, _ptr(gate_out),
+        _ptr(cache), dtype_code(cache.dtype), _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
+        _i32(block_table, "block_table"), block_table.shape[1], n_tokens, _stream())
+    _check(rc, "latent_prep")
+
+
+# ---- routed experts -----------------------------------------------------------------------------------------------
+
+@_profiled(lambda a, facts: (a["n_tokens"] * (a["z"].shape[1] * 4 + a["top"] * 12), a["n_tokens"] * a["z"].shape[1] * 8))
+def moe_route(z: torch.Tensor, bias: Optional[torch.Tensor], slot_of_token: torch.Tensor, n_tokens: int, top: int,
+              ids: torch.Tensor, weights: torch.Tensor, place: torch.Tensor, counts: torch.Tensor):
+    """z float32 [T, E] router logits -> per token the ``top`` experts by sigmoid(z) + bias (``ids`` int32 [T, top],
+    -1 for padding tokens), their weights sigmoid(z) (float32 [T, top]) and each choice's place among its expert's
+    rows (``place``); ``counts`` int32 [E], zero on entry, ends as the rows of every expert."""
+    E = z.shape[1]
+    if z.dtype != torch.float32 or z.stride(1) != 1:
+        raise KernelError("moe_route: router logits must be float32 with unit inner stride")
+    for t, name in ((ids, "ids"), (place, "place")):
+        if t.dtype != torch.int32 or not t.is_contiguous() or t.numel() < n_tokens * top:
+            raise KernelError(f"moe_route: {name} must be contiguous int32 [T, top]")
+    if weights.dtype != torch.float32 or not weights.is_contiguous() or weights.numel() < n_tokens * top:
+        raise KernelError("moe_route: weights must be contiguous float32 [T, top]")
+    if counts.dtype != torch.int32 or counts.numel() != E or (bias is not None and bias.numel() != E):
+        raise KernelError("moe_route: counts (int32) and bias must be [E]")
+    rc = _lib().rb_moe_route(_ptr(z), z.stride(0), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+                             _i32(slot_of_token, "slot_of_token"), n_tokens, E, top, _ptr(ids), _ptr(weights),
+                             _ptr(place), _ptr(counts), _stream())
+    _check(rc, "moe_route")
+
+
+def moe_plan(counts: torch.Tensor, tile_rows: int, starts: torch.Tensor, tile_group: torch.Tensor):
+    """Every expert's rows start at a multiple of ``tile_rows``: ``starts`` int32 [E + 1]; ``tile_group`` int32
+    [max tiles] names each tile's expert (-1: unused)."""
+    E = counts.numel()
+    if starts.dtype != torch.int32 or starts.numel() != E + 1 or tile_group.dtype != torch.int32:
+        raise KernelError("moe_plan: starts must be int32 [E + 1], tile_group int32")
+    _check(_lib().rb_moe_plan(_ptr(counts), E, int(tile_rows), tile_group.numel(), _ptr(starts), _ptr(tile_group),
+                              _stream()), "moe_plan")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["x"].shape[1] * _esz(a["x"]) * (1 + a["top"]), 0))
+def moe_gather(x: torch.Tensor, ids: torch.Tensor, place: torch.Tensor, starts: torch.Tensor, n_tokens: int, top: int,
+               rows: torch.Tensor, row_of: torch.Tensor):
+    """Copy token t's row of ``x`` [T, H] to each of its ``top`` places in ``rows`` [R, H]; ``row_of`` int32 [T, top]
+    receives the places (-1 for padding tokens)."""
+    if x.dtype != rows.dtype or not x.is_contiguous() or not rows.is_contiguous() or x.shape[1] != rows.shape[1]:
+        raise KernelError("moe_gather: x and rows must be contiguous, of one type and width")
+    _check(_lib().rb_moe_gather(_ptr(x), dtype_code(x.dtype), x.shape[1], _ptr(ids), _ptr(place), _ptr(starts), n_tokens,
+                                top, _ptr(rows), _ptr(row_of), _stream()), "moe_gather")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["out"].shape[1] * 4 * (1 + a["top"]), a["n_tokens"] * a["out"].shape[1] * 2 * a["top"]))
+def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, n_tokens: int, top: int, out: torch.Tensor):
+    """out [T, H] float32 = sum over a token's choices j of weights[t, j] * y[row_of[t, j]] (y float32 [R, H])."""
+    if y.dtype != torch.float32 or out.dtype != torch.float32 or y.stride(1) != 1 or not out.is_contiguous() or \
+            y.shape[1] != out.shape[1]:
+        raise KernelError("moe_combine: y and out must be float32 of one width")
+    _check(_lib().rb_moe_combine(_ptr(y), y.stride(0), _ptr(row_of), _ptr(weights), n_tokens, top, _ptr(out),
+                                 out.shape[1], _stream()), "moe_combine")
+
+
+# ---- many small products in one launch ----------------------------------------------------------------------------
+
+@_profiled(lambda a, facts: (a["w"].numel() * _esz(a["w"]) + a["m"] * a["w"].shape[0] * (a["w"].shape[2] * _esz(a["x"])
+                                                                                           + a["w"].shape[1] * _esz(a["out"])),
+                             2 * a["m"] * a["w"].shape[0] * a["w"].shape[1] * a["w"].shape[2]))
+def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m: int, row_scale: Optional[torch.Tensor] = None):
+    """Per-head products: out[t, g * N : (g + 1) * N] = x[t, g * K : (g + 1) * K] . w[g]^T for w [G, N, K]; rows may be
+    strided.  ``row_scale`` float32 [T, G] multiplies head g's result for row t."""
+    G, N, K = w.shape
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or x.shape[-1] < G * K or out.shape[-1] < G * N or not w.is_contiguous():
+        raise KernelError("head_matmul: shapes or strides do not fit")
+    if row_scale is not None and (row_scale.dtype != torch.float32 or not row_scale.is_contiguous() or row_scale.shape[-1] != G):
+        raise KernelError("head_matmul: row_scale must be contiguous float32 [T, G]")
+    rc = _lib().rb_grouped_matmul(_ptr(x), dtype_code(x.dtype), x.stride(0), K, _ptr(w), dtype_code(w.dtype), N * K,
+                                  _ptr(out), dtype_code(out.dtype), out.stride(0), N, m, N, K, G, None, 0,
+                                  _ptr(row_scale), G, _stream())
+    _check(rc, "head_matmul")
+
+
+@_profiled(lambda a, facts: (a["w"].numel() * _esz(a["w"]) + a["x"].shape[0] * (a["w"].shape[2] * _esz(a["x"])
+                                                                               + a["w"].shape[1] * _esz(a["out"])),
+                             2 * a["x"].shape[0] * a["w"].shape[1] * a["w"].shape[2]))
+def tile_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, tile_rows: int):
+    """Products by tiles of sorted rows: rows i * tile_rows .. of ``x`` [R, K] are multiplied with
+    w[tile_group[i]] ([G, N, K]) into the same rows of ``out`` [R, N]; a tile of group -1 is skipped."""
+    G, N, K = w.shape
+    R = x.shape[0]
+    if x.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != K or out.shape[1] != N or out.shape[0] != R or \
+            not w.is_contiguous() or R % tile_rows or tile_group.numel() < R // tile_rows:
+        raise KernelError("tile_matmul: shapes or strides do not fit")
+    rc = _lib().rb_grouped_matmul(_ptr(x), dtype_code(x.dtype), x.stride(0), 0, _ptr(w), dtype_code(w.dtype), N * K,
+                                  _ptr(out), dtype_code(out.dtype), out.stride(0), 0, R, N, K, G,
+                                  _i32(tile_group, "tile_group"), int(tile_rows), None, 0, _stream())
+    _check(rc, "tile_matmul")

@@ -8,14 +8,16 @@ from .base import (
 )
 from .linear import Linear
 from .norm import RMSNorm
-from .position import NoPosition, RotaryNeox
+from .position import NoPosition, RotaryNeox, SinusoidPosition
 from .attention import Attention
 from .mlp import GatedMLP
-from .block import PreNormBlock
+from .latent_attention import LatentAttention
+from .routed_mlp import RoutedMLP
+from .block import PreNormBlock, SandwichNormBlock
 
 __all__ = [
     "BuildEnv", "DeferredNorm", "ResidualSink", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "build_block",
     "build_feed_forward", "build_mixer", "build_norm", "build_position", "register_arrangement",
     "register_feed_forward", "register_mixer", "register_norm", "register_position", "registered",
-    "Linear", "RMSNorm", "NoPosition", "RotaryNeox", "Attention", "GatedMLP", "PreNormBlock",
+    "Linear", "RMSNorm", "NoPosition", "RotaryNeox", "Attention", "GatedMLP", "PreNormBlock", "LatentAttention", "RoutedMLP", "SandwichNormBlock", "SinusoidPosition",
 ]

@@ -207,40 +207,47 @@ class Attention(Mixer):
             rowscale=rowscale, row_width=row_width)
 
     def attend(self, q, out, batch, view, window):
-        """Softmax attention of the step's queries over the cache.  One token per sequence:
-        keys split in fixed chunks, partial results merged; otherwise whole rows."""
-        if batch.is_decode:
-            chunk = DECODE_CHUNK
-            T = batch.n_tokens
-            n_pages = max(1, (batch.max_kv_len + chunk - 1) // chunk)
-            groups = self.nkv * ((self.nq // self.nkv + 15) // 16)
-            n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages, q.device)
-            acc = ml = None
-            if n_pages > 1:
-                parts = max(n_pages, n_blocks)
-                acc = torch.empty((T, self.nq, parts, self.hd), dtype=torch.float32, device=q.device)
-                ml = torch.empty((T, self.nq, parts, 2), dtype=torch.float32, device=q.device)
-            fast = kernels.attention_decode(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
-                                            batch.kv_len, batch.n_seqs, self.nq, self.nkv, self.hd, self.scale,
-                                            window, n_blocks, acc, ml, ppb)
-            n_chunks = n_pages
-            if fast:
-                return
-            if n_chunks > 1:
-                kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
-                                          batch.kv_len, batch.n_seqs, 1, self.nq, self.nkv, self.hd, self.scale,
-                                          window, chunk, n_chunks, acc, ml)
-                kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, self.nq, self.hd,
-                                        chunk, n_chunks, window)
-                return
-        if kernels.attention_prefill_tc5(q, batch.n_tokens, out, view.k, view.v, view.block_table, batch.seq_slot,
-                                         batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv,
-                                         self.hd, self.scale, window, max_kv_len=batch.max_kv_len):
+        """Softmax attention of the step's queries over the cache (see ``paged_attention``)."""
+        paged_attention(q, out, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hd, self.scale, window)
+
+
+def paged_attention(q, out, batch, k_cache, v_cache, block_table, nq, nkv, hd, scale, window):
+    """Softmax attention of the step's queries (rows of nq heads of ``hd``) over paged keys and values
+    [pages, nkv, 64, hd], causal, inside ``window`` when it is not 0.  One token per sequence:
+    keys split in fixed chunks, partial results merged; otherwise whole rows.  Any mixer whose cache is
+    such pages calls this (keys and values may be the same tensor)."""
+    if batch.is_decode:
+        chunk = DECODE_CHUNK
+        T = batch.n_tokens
+        n_pages = max(1, (batch.max_kv_len + chunk - 1) // chunk)
+        groups = nkv * ((nq // nkv + 15) // 16)
+        n_blocks, ppb = kernels.decode_split(batch.n_seqs, groups, n_pages, q.device)
+        acc = ml = None
+        if n_pages > 1:
+            parts = max(n_pages, n_blocks)
+            acc = torch.empty((T, nq, parts, hd), dtype=torch.float32, device=q.device)
+            ml = torch.empty((T, nq, parts, 2), dtype=torch.float32, device=q.device)
+        fast = kernels.attention_decode(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                                        batch.kv_len, batch.n_seqs, nq, nkv, hd, scale,
+                                        window, n_blocks, acc, ml, ppb)
+        n_chunks = n_pages
+        if fast:
             return
-        if kernels.attention_prefill(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
-                                     batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,
-                                     self.scale, window):
+        if n_chunks > 1:
+            kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                                      batch.kv_len, batch.n_seqs, 1, nq, nkv, hd, scale,
+                                      window, chunk, n_chunks, acc, ml)
+            kernels.attention_merge(acc, ml, out, batch.positions, batch.slot_of_token, T, nq, hd,
+                                    chunk, n_chunks, window)
             return
-        kernels.attention_generic(q, out, view.k, view.v, view.block_table, batch.seq_slot, batch.cu_q,
-                                  batch.kv_len, batch.n_seqs, batch.max_q_len, self.nq, self.nkv, self.hd,
-                                  self.scale, window)
+    if kernels.attention_prefill_tc5(q, batch.n_tokens, out, k_cache, v_cache, block_table, batch.seq_slot,
+                                     batch.cu_q, batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv,
+                                     hd, scale, window, max_kv_len=batch.max_kv_len):
+        return
+    if kernels.attention_prefill(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                                 batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
+                                 scale, window):
+        return
+    kernels.attention_generic(q, out, k_cache, v_cache, block_table, batch.seq_slot, batch.cu_q,
+                              batch.kv_len, batch.n_seqs, batch.max_q_len, nq, nkv, hd,
+                              scale, window)

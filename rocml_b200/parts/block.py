@@ -105,3 +105,92 @@ def _takes(part, batch) -> bool:
 
 def _defer_enabled() -> bool:
     return os.environ.get("RB_DEFER", "1") != "0"
+
+
+@register_arrangement("sandwich_norm")
+class SandwichNormBlock:
+    """x += post1(mixer(norm1(x))); x += post2(ff(norm2(x))): a norm before and after each sublayer.
+
+    A sublayer's result (a delta, possibly as partial sums) is normalised on its own before it joins the
+    residual stream, so it cannot ride along to the next norm as a pre-norm block's delta does.  One
+    kernel adds the partial sums, normalises them, adds into the 32-bit residual and normalises that for
+    the sublayer that follows.  The block leaves nothing pending.  A layer without a feed-forward has
+    only the first half."""
+
+    chains = True          # forward() accepts next_block
+
+    def __init__(self, spec: LayerSpec, hidden: int, env: BuildEnv, mixer_spec=None):
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and spec.ff_post_norm is None):
+            from ..errors import ConfigError
+            raise ConfigError("a sandwich_norm layer needs a post norm for each of its sublayers")
+        self.spec = spec
+        self.prefix = spec.prefix
+        self.env = env
+        self.hidden = hidden
+        self.mixer_norm = build_norm(spec.mixer_norm, hidden, env)
+        self.mixer = build_mixer(mixer_spec or spec.mixer, hidden, env)
+        self.mixer_post = build_norm(spec.mixer_post_norm, hidden, env)
+        self.ff = self.ff_norm = self.ff_post = None
+        if spec.feed_forward is not None:
+            self.ff_norm = build_norm(spec.ff_norm, hidden, env)
+            self.ff = build_feed_forward(spec.feed_forward, hidden, env)
+            self.ff_post = build_norm(spec.ff_post_norm, hidden, env)
+
+    def _parts(self):
+        p, s = self.prefix, self.spec
+        out = [(self.mixer_norm, f"{p}.{s.mixer_norm_name}"), (self.mixer, f"{p}.{s.mixer_name}"),
+               (self.mixer_post, f"{p}.{s.mixer_post_norm_name}")]
+        if self.ff is not None:
+            out += [(self.ff_norm, f"{p}.{s.ff_norm_name}"), (self.ff, f"{p}.{s.ff_name}"),
+                    (self.ff_post, f"{p}.{s.ff_post_norm_name}")]
+        return out
+
+    def declare(self) -> List[TensorDecl]:
+        return [d for part, name in self._parts() for d in part.declare(name)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for part, name in self._parts():
+            part.load(tensors, name)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part, _ in self._parts())
+
+    def weight_bytes(self) -> int:
+        return sum(part.weight_bytes() for part, _ in self._parts())
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        half1 = self.mixer_norm.workspace_bytes(n_tokens) + self.mixer.workspace_bytes(n_tokens)
+        half2 = 0 if self.ff is None else self.ff_norm.workspace_bytes(n_tokens) + self.ff.workspace_bytes(n_tokens)
+        return max(half1, half2)
+
+    def cost(self, q_lens, kv_lens):
+        parts = [part.cost(q_lens, kv_lens) for part, _ in self._parts()]
+        return sum(p[0] for p in parts), sum(p[1] for p in parts)
+
+    def _post(self, resid, delta, post, nxt, T):
+        """resid += post(delta); returns nxt(resid) when a norm follows."""
+        from .. import kernels
+        for n in (post, nxt):
+            if n is not None and not hasattr(n, "weight"):
+                raise NotImplementedError("sandwich_norm is built for norms with a weight vector and an eps (rmsnorm)")
+        out = None
+        if nxt is not None:
+            out = torch.empty((T, self.hidden), dtype=self.env.act_dtype, device=resid.device)
+        kernels.postnorm_add_norm(resid, delta, post.weight, post.eps, nxt.weight if nxt is not None else None,
+                                  nxt.eps if nxt is not None else 0.0, out)
+        return out
+
+    def forward(self, resid, pending, batch, view, next_block=None):
+        T = batch.n_tokens
+        with scope(op="mixer_norm"):
+            xn = self.mixer_norm.forward(resid, pending, T)      # (adds whatever a different kind of layer before left pending)
+        delta = self.mixer.forward(xn, batch, view)
+        with scope(op="mixer_post_norm"):
+            xn = self._post(resid, delta, self.mixer_post, self.ff_norm, T)
+        if self.ff is None:
+            return None
+        delta = self.ff.forward(xn, batch)
+        with scope(op="ff_post_norm"):
+            self._post(resid, delta, self.ff_post, None, T)
+        return None

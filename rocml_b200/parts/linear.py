@@ -82,6 +82,19 @@ class Linear:
         if self.has_bias:
             self.bias = torch.cat([tensors[f"{prefix}{n}.bias"].float() for n in self.names]).contiguous()
 
+    def pad_rows(self, multiple: int) -> None:
+        """Append zero rows to the loaded weight until its row count is a multiple of ``multiple``: a stack of
+        odd width then still meets the tensor-core product's alignment (rows of the result on 16 bytes).  The
+        product gets as many more columns, which are zero."""
+        pad = -self.n % multiple
+        if not pad or self.weight is None:
+            return
+        self.weight = torch.cat([self.weight, self.weight.new_zeros((pad, self.k))], dim=0).contiguous()
+        if self.bias is not None:
+            self.bias = torch.cat([self.bias, self.bias.new_zeros(pad)]).contiguous()
+        self.outs.append(pad)
+        self.n += pad
+
     def interleave_pairs(self) -> bool:
         """For a stack of two equally wide projections (gate, up): reorder the rows so that blocks
         of 16 gate rows alternate with the 16 up rows of the same outputs.  The tensor-core

@@ -51,3 +51,26 @@ class RotaryNeox(PositionEncoding):
         if key not in batch.scratch:
             batch.scratch[key] = kernels.rope_table(batch.positions, self.inv_freq, batch.n_tokens)
         return batch.scratch[key]
+
+
+@register_position("sinusoid")
+class SinusoidPosition(PositionEncoding):
+    """A position vector added to the embedding output (a model's ``input_position``), not a rotation inside
+    a mixer: entry 2i is sin(pos * theta^(-2i / width)), entry 2i + 1 the cosine of the same angle.  The
+    exponent and the power are evaluated in double precision and rounded once to float32; the angle and its
+    sine and cosine are 32-bit, in the embedding kernel.  ``head_dim`` here is the model's width."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PositionSpec, head_dim: int, env: BuildEnv):
+        if not spec.theta > 0:
+            raise ConfigError(f"the sinusoid's base must be positive, found {spec.theta}")
+        self.width = head_dim
+        self.theta = float(spec.theta)
+        self.rot_dim = 0
+        i = torch.arange((head_dim + 1) // 2, dtype=torch.float64)
+        inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / head_dim)
+        self.inv_freq = inv.to(torch.float32).to(env.device)
+
+    def cos_sin(self, batch):
+        return None

@@ -1,0 +1,153 @@
+"""Routed feed-forward: a router and many small gated feed-forwards, of which a token uses a few.
+
+    z = Wr h (32-bit);  s = sigmoid(z);  chosen = the ``top`` experts by s + bias;  weight_e = s_e
+    expert e:  y = act(Wgate_e h, Wup_e h);  out_e = Wdown_e y
+    result = sum over the chosen of weight_e * out_e
+
+``activation`` "silu": silu(g) * u.  "clamped_swish": g = min(g, limit), u = clamp(u, -limit, limit),
+g * sigmoid(alpha * g) * (u + 1).  ``choice_bias`` adds a per-expert vector to the scores for the choice
+only; the weights are the scores themselves, renormalised over the chosen if ``renormalize`` says so.
+
+How a step runs, without the host ever learning who chose what (so a decode step is one CUDA graph):
+the router's product, one kernel that scores, chooses and counts, one that lays every expert's rows out
+from a multiple of the row tile, one that copies each token's row to its places, two products over
+tiles of those rows (every tile names its expert's weight), the activation between them, and a
+weighted sum back into token order.  The row tile is 16 for few tokens and 64 beyond.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels
+from ..config.specs import FeedForwardSpec, tensor_names
+from ..errors import ConfigError
+from ..profile import scope
+from ..weights.decl import TensorDecl
+from .base import BuildEnv, FeedForward, register_feed_forward
+
+TENSOR_NAMES = {"router": "gate", "choice_bias": "e_score_correction_bias", "expert": "experts.{e}.", "gate": "gate_proj",
+                "up": "up_proj", "down": "down_proj"}
+
+SMALL_TILE, LARGE_TILE = 16, 64
+SMALL_TILE_MAX_ROWS = 256      # token-choices up to which the 16-row tile is used
+
+
+@register_feed_forward("routed_mlp")
+class RoutedMLP(FeedForward):
+    graph_safe = True
+
+    def __init__(self, spec: FeedForwardSpec, hidden: int, env: BuildEnv):
+        p = spec.params
+        self.env = env
+        self.hidden = hidden
+        self.experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.inter = int(p["intermediate"])
+        if not 0 < self.top <= self.experts or self.experts > 512 or self.inter <= 0:
+            raise ConfigError(f"routed_mlp: {self.top} of {self.experts} experts of {self.inter} is not supported "
+                              "(1 to 512 experts, at least one and at most all of them a token)")
+        self.act = p.get("activation", "silu")
+        if self.act not in kernels.GATED_ACTS:
+            raise ConfigError(f"routed_mlp: activation {self.act!r} is not built (known: {sorted(kernels.GATED_ACTS)})")
+        self.limit = float(p.get("limit", 0.0))
+        self.alpha = float(p.get("alpha", 1.0))
+        if self.act == "clamped_swish" and not self.limit > 0:
+            raise ConfigError("routed_mlp: clamped_swish needs a positive limit")
+        if p.get("score", "sigmoid") != "sigmoid":
+            raise ConfigError(f"routed_mlp: score {p.get('score')!r} is not built (only 'sigmoid')")
+        if p.get("renormalize", False):
+            raise ConfigError("routed_mlp: renormalised weights are not built")
+        self.has_bias = bool(p.get("choice_bias", False))
+        try:
+            self.names = tensor_names(p, TENSOR_NAMES)
+        except ValueError as e:
+            raise ConfigError(f"routed_mlp: {e}") from None
+        self.router: Optional[torch.Tensor] = None         # float32 [experts, hidden]
+        self.choice_bias: Optional[torch.Tensor] = None    # float32 [experts]
+        self.gate_up: Optional[torch.Tensor] = None        # [experts, 2 * inter, hidden]: gate rows, then up rows
+        self.down: Optional[torch.Tensor] = None           # [experts, hidden, inter]
+
+    def _expert(self, prefix: str, e: int, role: str) -> str:
+        return f"{prefix}{self.names['expert'].format(e=e)}{self.names[role]}.weight"
+
+    def declare(self, prefix: str) -> List[TensorDecl]:
+        out = [TensorDecl(f"{prefix}{self.names['router']}.weight", (self.experts, self.hidden), "matrix")]
+        if self.has_bias:
+            out.append(TensorDecl(f"{prefix}{self.names['choice_bias']}.weight", (self.experts,), "bias"))
+        for e in range(self.experts):
+            out += [TensorDecl(self._expert(prefix, e, "gate"), (self.inter, self.hidden), "matrix"),
+                    TensorDecl(self._expert(prefix, e, "up"), (self.inter, self.hidden), "matrix"),
+                    TensorDecl(self._expert(prefix, e, "down"), (self.hidden, self.inter), "matrix")]
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
+        self.router = tensors[f"{prefix}{self.names['router']}.weight"].float().contiguous()     # the router is 32-bit
+        if self.has_bias:
+            self.choice_bias = tensors[f"{prefix}{self.names['choice_bias']}.weight"].float().contiguous()
+        gu = [torch.cat([tensors[self._expert(prefix, e, "gate")], tensors[self._expert(prefix, e, "up")]], dim=0)
+              for e in range(self.experts)]
+        self.gate_up = torch.stack(gu).contiguous()
+        self.down = torch.stack([tensors[self._expert(prefix, e, "down")] for e in range(self.experts)]).contiguous()
+
+    def weight_bytes(self) -> int:
+        """What a step reads at most: the router and the experts that can be chosen."""
+        esz = 4 if self.env.mode == "float32" else 2
+        return self.experts * self.hidden * 4 + self.experts * 3 * self.inter * self.hidden * esz
+
+    def _tile(self, n_tokens: int) -> int:
+        return SMALL_TILE if n_tokens * self.top <= SMALL_TILE_MAX_ROWS else LARGE_TILE
+
+    def _max_tiles(self, n_tokens: int) -> int:
+        """Every expert's rows start on a tile: at most one partly filled tile an expert that has rows."""
+        tile = self._tile(n_tokens)
+        return (n_tokens * self.top + tile - 1) // tile + min(self.experts, n_tokens * self.top)
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        esz = 4 if self.env.mode == "float32" else 2
+        rows = self._max_tiles(n_tokens) * self._tile(n_tokens)
+        return rows * (self.hidden * (esz + 4) + self.inter * 3 * esz) + n_tokens * (self.hidden * 4 + self.experts * 4)
+
+    def cost(self, q_lens, kv_lens):
+        T = sum(q_lens)
+        esz = 4 if self.env.mode == "float32" else 2
+        used = min(self.experts, T * self.top)
+        nbytes = self.experts * self.hidden * 4 + used * 3 * self.inter * self.hidden * esz
+        return nbytes, 2 * T * self.experts * self.hidden + 2 * T * self.top * 3 * self.inter * self.hidden
+
+    def forward(self, xn, batch):
+        T = batch.n_tokens
+        dev, act = self.env.device, self.env.act_dtype
+        E, top = self.experts, self.top
+        tile = self._tile(T)
+        max_tiles = self._max_tiles(T)
+        rows = max_tiles * tile
+        z = torch.empty((T, E), dtype=torch.float32, device=dev)
+        with scope(op="router"):
+            kernels.gemm_generic(xn, self.router, z, None, T)
+        ids = torch.empty((T, top), dtype=torch.int32, device=dev)
+        place = torch.empty((T, top), dtype=torch.int32, device=dev)
+        weights = torch.empty((T, top), dtype=torch.float32, device=dev)
+        counts = torch.zeros((E,), dtype=torch.int32, device=dev)
+        starts = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+        tile_group = torch.empty((max_tiles,), dtype=torch.int32, device=dev)
+        row_of = torch.empty((T, top), dtype=torch.int32, device=dev)
+        with scope(op="route"):
+            kernels.moe_route(z, self.choice_bias, batch.slot_of_token, T, top, ids, weights, place, counts)
+            kernels.moe_plan(counts, tile, starts, tile_group)
+            xs = torch.empty((rows, self.hidden), dtype=act, device=dev)
+            kernels.moe_gather(xn, ids, place, starts, T, top, xs, row_of)
+        gu = torch.empty((rows, 2 * self.inter), dtype=act, device=dev)
+        with scope(op="experts_gate_up"):
+            kernels.tile_matmul(xs, self.gate_up, gu, tile_group, tile)
+        y = torch.empty((rows, self.inter), dtype=act, device=dev)
+        with scope(op="experts_act"):
+            kernels.gated_act(gu, y, self.act, self.limit, self.alpha)
+        out_rows = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
+        with scope(op="experts_down"):
+            kernels.tile_matmul(y, self.down, out_rows, tile_group, tile)
+        delta = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
+        with scope(op="experts_sum"):
+            kernels.moe_combine(out_rows, row_of, weights, T, top, delta[0])
+        return delta
