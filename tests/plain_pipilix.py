@@ -83,11 +83,35 @@ def expert_ff(h, w, pre, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[pre + "down"].t()
 
 
+MARGINS = None      # a list, while a test wants to know how close the routers' choices were
+
+
 def route(h, w, pre, top):
     """(chosen [T, top] expert numbers, weights [T, top]): sigmoid scores; the correction only chooses."""
     s = torch.sigmoid(h @ w[pre + "router"].t())
-    chosen = torch.topk(s + w[pre + "correction"], top, dim=-1).indices
+    choice = s + w[pre + "correction"]
+    chosen = torch.topk(choice, top, dim=-1).indices
+    if MARGINS is not None and top < choice.shape[-1]:
+        best = torch.topk(choice, top + 1, dim=-1).values
+        MARGINS.append(best[:, top - 1] - best[:, top])        # per token: the last chosen over the first left out
     return chosen, torch.gather(s, 1, chosen)
+
+
+def closest_calls(w, cfg, ids):
+    """Per token, the smallest margin by which any router of any layer run chose its last expert over the next
+    (infinite where no router has a choice to make).  A token whose margin is within rounding may be routed otherwise
+    by an implementation that rounds otherwise, and so may every later token that sees it."""
+    global MARGINS
+    MARGINS = []
+    try:
+        forward(w, cfg, ids, torch.float64)
+        got = MARGINS
+    finally:
+        MARGINS = None
+    out = torch.full((len(ids),), float("inf"), dtype=torch.float64)
+    for m in got:
+        out = torch.minimum(out, m)
+    return out
 
 
 def routed_ff(h, w, pre, experts, top, limit):

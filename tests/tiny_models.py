@@ -71,3 +71,71 @@ def write_model(folder, cfg_dict, seed, std=None):
 def prompt(seed, n, vocab):
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+# ---- Pipilix: small configurations that differ in every size, option and constant ---------------------------------
+def _latent(heads, dim, vdim, rank, window, scale):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": rank, "scale": scale, "mask": {"size": window}}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def _moe(ff, limit, experts, top):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+
+
+def _layer(mixer, mlp):
+    return {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+
+
+# PA: a loop from the first layer that runs three times, a layer without a feed-forward, unequal layers
+PIPILIX_A = {
+    "architecture": "Pipilix", "vocab": 200, "width": 64, "embedding": {"scale": 3.0}, "norm": {"eps": 1e-6},
+    "logit_scale": 0.5, "loop": {"start": 0, "stop": 2, "times": 3},
+    "layers": [_layer(_latent(4, 16, 8, 32, 9, 0.3), _dense(96)),
+               _layer(_latent(2, 24, 40, 24, 70, 0.2), _moe(40, 0.7, 5, 2)),
+               _layer(_latent(4, 16, 16, 48, 200, 0.25), None)],
+}
+# PB: no loop; latents of 64 and 128 (the sizes the bfloat16 attention kernels take), one expert a token of sixteen,
+# a window of exactly one page
+PIPILIX_B = {
+    "architecture": "Pipilix", "vocab": 333, "width": 128, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+    "logit_scale": 1.0,
+    "layers": [_layer(_latent(8, 32, 32, 64, 100, 0.18), _moe(64, 2.0, 16, 1)),
+               _layer(_latent(3, 64, 48, 128, 64, 0.125), _dense(160)),
+               _layer(_latent(9, 16, 24, 64, 300, 0.25), _moe(48, 1.5, 4, 3))],
+}
+# PC: sizes that are multiples of four only, every expert chosen, a window of one token, a loop that runs once
+PIPILIX_C = {
+    "architecture": "Pipilix", "vocab": 97, "width": 72, "embedding": {"scale": 7.5}, "norm": {"eps": 3e-5},
+    "logit_scale": 3.0, "loop": {"start": 1, "stop": 2, "times": 1},
+    "layers": [_layer(_latent(3, 12, 20, 20, 1, 0.5), _moe(28, 0.4, 3, 3)),
+               _layer(_latent(5, 8, 4, 36, 17, 0.35), _dense(52)),
+               _layer(_latent(1, 40, 12, 28, 33, 0.15), _moe(20, 1.0, 7, 2))],
+}
+PIPILIX = {"PA": PIPILIX_A, "PB": PIPILIX_B, "PC": PIPILIX_C}
+
+
+def write_pipilix(folder, cfg_dict, seed, std=0.05, sharp=1.0, bias_std=0.5, router_gain=3.0):
+    """A Pipilix model folder with random weights.  ``std``: the matrices' standard deviation; ``sharp``
+    multiplies the query and key-unfolding matrices, so that the softmax picks few keys and a key wrongly
+    seen or missed moves the result; ``bias_std``: the routers' choice biases (large enough to change
+    choices); ``router_gain`` multiplies the routers, which spreads the scores (fewer near ties)."""
+    from safetensors.torch import load_file, save_file
+    write_model(folder, cfg_dict, seed)
+    path = os.path.join(folder, "model.safetensors")
+    w = load_file(path)
+    for k in w:
+        if w[k].dim() == 2:
+            f = std / 0.02
+            if k.endswith(".mix.q") or k.endswith(".mix.uk"):
+                f *= sharp
+            if k.endswith(".mlp.router"):
+                f *= router_gain
+            w[k] = (w[k].float() * f).to(torch.bfloat16)
+        elif k.endswith(".correction"):
+            w[k] = (w[k].float() * (bias_std / 0.02)).to(torch.bfloat16)
+    save_file(w, path)
+    return folder
