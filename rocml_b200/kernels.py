@@ -990,6 +990,7 @@ def moe_route(z: torch.Tensor, bias: Optional[torch.Tensor], slot_of_token: torc
     _check(rc, "moe_route")
 
 
+@_profiled(lambda a, facts: ((a["counts"].numel() * 2 + a["tile_group"].numel()) * 4, 0))
 def moe_plan(counts: torch.Tensor, tile_rows: int, starts: torch.Tensor, tile_group: torch.Tensor):
     """Every expert's rows start at a multiple of ``tile_rows``: ``starts`` int32 [E + 1]; ``tile_group`` int32
     [max tiles] names each tile's expert (-1: unused)."""

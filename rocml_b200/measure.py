@@ -10,6 +10,7 @@ workloads of the same kind, and the sweeps and timelines that the notes under ``
     python -m rocml_b200.measure float32                      the 32-bit path at the benchmark's layer sizes
     python -m rocml_b200.measure profile [--dtype float32]    the per-kernel table of --profile, random weights
     python -m rocml_b200.measure host [--model NAME]          what the Python host costs a decode step
+    python -m rocml_b200.measure compare [pipilix-2k|-4k]     a Pipilix size beside the dense decoder of equal size
 
 Everything is timed on the device with CUDA events after warm-up; weights are random, token ids
 seeded uniform-random (the reference's bench repeats a filler sentence for the same purpose,
@@ -99,10 +100,7 @@ def build_engine(layers, max_tokens, max_slots, model=None, dtype="bfloat16", ct
     from .engine import Engine, Model
     from .parts import BuildEnv
 
-    full = dict(CATALOG[model or MODEL].config)
-    n_full = full["num_hidden_layers"]
-    if layers:
-        full["num_hidden_layers"] = layers
+    full, n_full = with_layers(CATALOG[model or MODEL].config, layers)
     cfg = config_from_dict(full)
     dev = torch.device("cuda:0")
     with torch.cuda.device(dev):
@@ -110,6 +108,28 @@ def build_engine(layers, max_tokens, max_slots, model=None, dtype="bfloat16", ct
         m.load_random(seed=0)
         eng = Engine(m, max_tokens=max_tokens, max_slots=max_slots, max_step_tokens=4096, max_seq_len=ctx or CTX)
     return cfg, n_full, eng
+
+
+def with_layers(config: dict, layers: int):
+    """(a copy of a catalog entry's config.json cut to ``layers`` layers (0: all), the layers it has).  A config
+    that lists its layers keeps the first ones, and a looped span is cut to what is left of it."""
+    full = json.loads(json.dumps(config))
+    if "num_hidden_layers" in full:
+        n_full = full["num_hidden_layers"]
+        if layers:
+            full["num_hidden_layers"] = layers
+            if full.get("layer_types"):
+                full["layer_types"] = full["layer_types"][:layers]
+        return full, n_full
+    n_full = len(full["layers"])
+    if layers and layers < n_full:
+        full["layers"] = full["layers"][:layers]
+        loop = full.get("loop")
+        if loop:
+            loop["stop"] = min(loop["stop"], layers)
+            if loop["start"] >= loop["stop"]:
+                del full["loop"]
+    return full, n_full
 
 
 def prompts(n, length, vocab, seed):
@@ -529,6 +549,90 @@ def profile_table(model=None, layers=0, batch=BATCH, dtype="bfloat16", prompt=PR
     print(to_human(prof.report(), layers=by_layer))
 
 
+# ---- one architecture beside its closest relative at equal size --------------------------------------------------
+PAIRS = {"pipilix-2k": "qwen3-like-2k", "pipilix-4k": "qwen3-like-4k"}
+
+
+def _by_op(report):
+    """{phase: {operation: {ms, share, efficiency, bound}}} of a profile's report, and each phase's total."""
+    out = {}
+    for ph in report["phases"]:
+        rows = {r["label"]: {"ms": round(r["elapsed_ms"], 4), "pct": round(r["pct_of_phase_time"], 1),
+                             "eff": round(r["efficiency"], 3), "bound": r["bound"]} for r in ph["by_op"]}
+        rows["(all)"] = {"ms": round(ph["total"]["elapsed_ms"], 4), "pct": 100.0, "eff": round(ph["total"]["efficiency"], 3),
+                         "bound": ph["total"]["bound"]}
+        out[ph["phase"]] = rows
+    return out
+
+
+def model_point(name, layers=0, steps=32, warmup=4, profile=True, tables=None):
+    """Prompt and decode throughput of a catalog entry's layer sizes (random weights): one prompt of PREFILL_TOKENS
+    tokens, decode at batch BATCH after prompts of PROMPT tokens, each against the device's limits (what the model's
+    parts say a step must at least move and do), and, from one profiled prompt and four profiled decode steps, the
+    time and the efficiency of every kind of kernel."""
+    import torch
+    from . import StepEntry
+    from .profile import Profiler, to_human
+    pk = peaks()
+    cfg, n_full, eng = build_engine(layers, BATCH * (PROMPT + 64 * 3) + PREFILL_TOKENS + 64, BATCH + 1, model=name)
+    spec = eng.model.spec
+    vocab = spec.vocab
+    prefill_ms = time_prefill(eng, vocab)
+    pf = prefill_flops(eng, PREFILL_TOKENS)
+    ms, ctx_tokens, _ = time_decode(eng, BATCH, steps, warmup, vocab, seed=3)
+    bytes_step = eng.model.step_cost([1] * BATCH, [int(ctx_tokens / BATCH)] * BATCH, BATCH)[0]
+    rec = {"model": name, "layer_runs": len(spec.schedule), "layers_full": n_full, "width": spec.hidden,
+           "weights_gb": round(torch.cuda.memory_allocated() / 1e9, 2),
+           "prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(prefill_ms, 3),
+           "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1),
+           "prefill_tflops": round(pf / (prefill_ms * 1e-3) / 1e12, 1),
+           "prefill_frac_bf16": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+           "decode_batch": BATCH, "decode_ms": round(ms, 4), "decode_tok_s": round(BATCH * 1000.0 / ms, 1),
+           "decode_gb_step": round(bytes_step / 1e9, 3),
+           "decode_frac_hbm": round(bytes_step / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+    if profile:
+        ps = prompts(BATCH, PROMPT + 4, vocab, 5)
+        long = prompts(1, PREFILL_TOKENS, vocab, 6)[0]
+
+        def run():
+            slot = eng.new_sequence()
+            eng.step([StepEntry(slot, long, [PREFILL_TOKENS - 1])])
+            eng.release(slot)
+            slots = [eng.new_sequence() for _ in ps]
+            eng.step([StepEntry(s, p[:PROMPT], [PROMPT - 1]) for s, p in zip(slots, ps)])
+            for t in range(4):
+                eng.step([StepEntry(s, [p[PROMPT + t]], [0]) for s, p in zip(slots, ps)])
+            for s in slots:
+                eng.release(s)
+        run()
+        with Profiler(eng.device) as prof:
+            run()
+        report = prof.report()
+        rec["kernels"] = _by_op(report)
+        if tables is not None:
+            tables.append(f"## {name}: {len(spec.schedule)} layer runs, one prompt of {PREFILL_TOKENS} tokens, {BATCH} prompts of "
+                          f"{PROMPT}, 4 decode steps at batch {BATCH}\n\n" + to_human(report))
+    del eng
+    torch.cuda.empty_cache()
+    return rec
+
+
+def compare(names=None, layers=0, steps=32, tables_path=None):
+    """Each Pipilix size beside the dense decoder of equal width, heads, layer runs and active feed-forward width."""
+    tables = [] if tables_path else None
+    out = {"workload": "pipilix", "peaks": peaks(), "pairs": []}
+    for name in names or sorted(PAIRS):
+        a = model_point(name, layers, steps, tables=tables)
+        b = model_point(PAIRS[name], layers, steps, tables=tables)
+        out["pairs"].append({"model": a, "beside": b,
+                             "prefill_ratio": round(a["prefill_tok_s"] / b["prefill_tok_s"], 3),
+                             "decode_ratio": round(a["decode_tok_s"] / b["decode_tok_s"], 3)})
+    if tables_path:
+        with open(tables_path, "w") as f:
+            f.write("\n\n".join(tables) + "\n")
+    return out
+
+
 def host_cost(model=None, layers=0, batches=(1, 8, 64), steps=64):
     """What the Python host costs a decode step: the step on the device alone (CUDA events around steps
     whose tokens never leave the device), the same through ``Engine.generate`` with the loop reading
@@ -579,13 +683,14 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m rocml_b200.measure", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=["sweep", "timeline", "sampler", "gemm-decode", "gemm-prefill", "workload", "float32",
-                                     "profile", "host"])
+                                     "profile", "host", "compare"])
     ap.add_argument("name", nargs="?", default=None, help="for workload: " + " or ".join(WORKLOADS))
     ap.add_argument("--model", default=MODEL, help="catalog entry whose layer sizes are used")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of timeline")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the entry has (0: all; timeline: 4)")
     ap.add_argument("--runs", type=int, default=1)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="of profile")
+    ap.add_argument("--tables", default=None, help="of compare: a file that receives the per-kernel tables")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length of profile; of timeline: list a prompt's step instead")
     args = ap.parse_args(argv)
     if args.what == "sweep":
@@ -605,6 +710,8 @@ def main(argv=None) -> int:
         host_cost(args.model, args.layers)
     elif args.what == "profile":
         profile_table(args.model, args.layers, args.batch, args.dtype, args.prompt)
+    elif args.what == "compare":
+        print(json.dumps(compare([args.name] if args.name else None, args.layers, tables_path=args.tables)))
     else:
         if args.name not in WORKLOADS:
             ap.error("workload needs one of: " + ", ".join(WORKLOADS))
