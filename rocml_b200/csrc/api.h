@@ -31,8 +31,9 @@ int rb_postnorm_add_norm(float* resid, const float* delta, int n_delta, long lon
                          int n_rows, int H, void* stream);
 
 // [gate | up] halves -> out; kind 0: silu(g) * u; kind 1: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u) + 1).
+// paired: gates and ups alternate in blocks of 16 columns instead of lying in two halves.
 int rb_gated_act(const void* in, int in_dtype, int n_in, long long in_stride, long long in_ld, void* out, int out_dtype,
-                 long long out_ld, int rows, int I, int kind, float limit, float alpha, void* stream);
+                 long long out_ld, int rows, int I, int kind, float limit, float alpha, int paired, void* stream);
 
 int rb_scale(float* x, long long n, float factor, void* stream);
 
@@ -43,7 +44,9 @@ int rb_latent_prep(const void* in, int in_dtype, int n_in, long long in_stride, 
                    void* cache, int act_dtype, const int* positions, const int* slot_of_token, const int* block_table,
                    int max_pages, int T, void* stream);
 
-// Routed experts (routing.cu).
+// Routed experts (routing.cu).  Router logits z[T, E] = x[T, K] . w[E, K]^T with 32-bit FMA, w float32.
+int rb_router_logits(const void* x, int x_dtype, long long ldx, const float* w, float* z, int ldz, int T, int E, int K,
+                     void* stream);
 int rb_moe_route(const float* z, int ldz, const void* bias, int bias_dtype, const int* slot_of_token, int T, int E,
                  int top, int* ids, float* weights, int* place, int* counts, void* stream);
 int rb_moe_plan(const int* counts, int E, int tile_rows, int max_tiles, int* starts, int* tile_group, void* stream);
@@ -97,6 +100,11 @@ int rb_gemm_tcgen05_qkv_rope(const void* x, const void* w, const float* bias, in
                              const int* slot_of_token, const int* block_table, int max_pages, const void* q_norm_w,
                              const void* k_norm_w, int norm_w_f32, float norm_eps, const float* cos_sin, int nq,
                              int nkv, int stages, int* status, void* stream);
+
+// The persistent product over tiles of 128 sorted rows, each with the weight of its group (see the definition).
+int rb_gemm_tcgen05_grouped(const void* x, const void* w, void* out, int out_dtype, int R, int N, int K, int groups,
+                            long long ldx, long long ldo, const int* tile_group, int gated, int act_kind,
+                            float act_limit, float act_alpha, int* status, void* stream);
 
 int rb_gemm_tcgen05_add(const void* x, const void* w, const float* bias, float* resid, int M, int N, int K,
                         long long ldx, long long ld_resid, int stages, int* status, void* stream);

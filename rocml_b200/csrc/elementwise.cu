@@ -531,22 +531,25 @@ extern "C" int rb_postnorm_add_norm(float* resid, const float* delta, int n_delt
 
 // ---- gated activations on a stacked [gate | up] product ------------------------------------------------
 // in: [S][rows, 2 * I] (S partial sums, added first, in order), gates in columns 0 .. I - 1 and ups in
-// I .. 2 I - 1; out: [rows, I].
+// I .. 2 I - 1, or, when `paired`, alternating in blocks of 16 columns (gate of output i at
+// (i / 16) * 32 + i % 16, its up 16 columns on); out: [rows, I].
 //   kind 0: silu(g) * u, silu(g) = g / (1 + exp(-g))
 //   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(alpha * g') * (u' + 1)
 template <typename IT, typename OT>
 __global__ void gated_act_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, size_t in_ld, OT* __restrict__ out,
-                                 size_t out_ld, int rows, int I, int kind, float limit, float alpha) {
+                                 size_t out_ld, int rows, int I, int kind, float limit, float alpha, int paired) {
     pdl_trigger();
     pdl_wait();
     const size_t n = (size_t)rows * I;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
         const int i = (int)(idx - t * I);
+        const int gi = paired ? (i >> 4) * 32 + (i & 15) : i;
+        const int up = paired ? 16 : I;
         float g = 0.f, u = 0.f;
         for (int s = 0; s < n_in; ++s) {
-            g += to_f32(in[(size_t)s * in_stride + t * in_ld + i]);
-            u += to_f32(in[(size_t)s * in_stride + t * in_ld + I + i]);
+            g += to_f32(in[(size_t)s * in_stride + t * in_ld + gi]);
+            u += to_f32(in[(size_t)s * in_stride + t * in_ld + gi + up]);
         }
         float v;
         if (kind == 0) {
@@ -562,9 +565,9 @@ __global__ void gated_act_kernel(const IT* __restrict__ in, int n_in, size_t in_
 
 extern "C" int rb_gated_act(const void* in, int in_dtype, int n_in, long long in_stride, long long in_ld, void* out,
                             int out_dtype, long long out_ld, int rows, int I, int kind, float limit, float alpha,
-                            void* stream) {
+                            int paired, void* stream) {
     if (rows <= 0 || I <= 0) return RB_OK;
-    if (n_in < 1 || kind < 0 || kind > 1) return RB_ERR_BAD_SIZE;
+    if (n_in < 1 || kind < 0 || kind > 1 || (paired && I % 16)) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t n = (size_t)rows * I;
     const int threads = 256;
@@ -573,13 +576,13 @@ extern "C" int rb_gated_act(const void* in, int in_dtype, int n_in, long long in
     typedef __nv_bfloat16 bf;
     if (in_dtype == RB_BF16 && out_dtype == RB_BF16)
         RB_LAUNCH((gated_act_kernel<bf, bf>), dim3(blocks), dim3(threads), 0, s, (const bf*)in, n_in, (size_t)in_stride,
-                  (size_t)in_ld, (bf*)out, (size_t)out_ld, rows, I, kind, limit, alpha);
+                  (size_t)in_ld, (bf*)out, (size_t)out_ld, rows, I, kind, limit, alpha, paired);
     else if (in_dtype == RB_F32 && out_dtype == RB_BF16)
         RB_LAUNCH((gated_act_kernel<float, bf>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride,
-                  (size_t)in_ld, (bf*)out, (size_t)out_ld, rows, I, kind, limit, alpha);
+                  (size_t)in_ld, (bf*)out, (size_t)out_ld, rows, I, kind, limit, alpha, paired);
     else if (in_dtype == RB_F32 && out_dtype == RB_F32)
         RB_LAUNCH((gated_act_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride,
-                  (size_t)in_ld, (float*)out, (size_t)out_ld, rows, I, kind, limit, alpha);
+                  (size_t)in_ld, (float*)out, (size_t)out_ld, rows, I, kind, limit, alpha, paired);
     else
         return RB_ERR_BAD_DTYPE;
     RB_LAUNCH_CHECK();

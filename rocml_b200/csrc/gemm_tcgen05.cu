@@ -82,6 +82,14 @@ struct Params {
     float norm_eps;
     const float2* cos_sin;        // [tokens][64] (cos, sin), or null
     int nq, nkv;
+    // persistent kernel, grouped: the rows of A are sorted by group, every group starting at a multiple of 128
+    // rows; row tile i is multiplied with the weight of group tile_group[i] (rows group * group_rows .. of the
+    // stacked B operand), a tile of group -1 is skipped.  b_rows is then one group's feature count.
+    const int* tile_group;
+    int group_rows;
+    // gated epilogues: 0 silu(g) * u; 1 min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)
+    int act_kind;
+    float act_limit, act_alpha;
 };
 
 // 16 consecutive outputs as 16-byte stores (dst is 16-byte aligned).
@@ -489,6 +497,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     const int n_total = m_tiles * n_tiles;
     const int n_kb = (p.K + BK - 1) / BK;
     constexpr int TMEM_COLS = 2 * C::TMEM_COLS;   // 512 at BN = 256
+    // grouped: which weight a row tile takes was decided by kernels before this one, so every role waits for
+    // them first; all three roles then skip the same tiles (group -1) and count only the others
+    const int* const tile_group = p.tile_group;
+    if (tile_group) rb::pdl_wait();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -510,9 +522,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             tma_prefetch_desc(&map_a);
             tma_prefetch_desc(&map_b);
             long long it = 0;          // K blocks issued so far, over all tiles: the ring's position
-            bool ok = true, waited = false;
+            bool ok = true, waited = tile_group != nullptr;
             for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x) {
-                const int a0 = (tile % m_tiles) * BM, b0 = (tile / m_tiles) * BN;
+                const int a0 = (tile % m_tiles) * BM;
+                int b0 = (tile / m_tiles) * BN;
+                if (tile_group) {
+                    const int grp = tile_group[tile % m_tiles];
+                    if (grp < 0) continue;
+                    b0 += grp * p.group_rows;
+                }
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = (int)(it % S);
                     const uint32_t ph = (uint32_t)((it / S) & 1);
@@ -550,9 +568,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             long long it = 0;
             int local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x, ++local) {
+            for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x) {
+                if (tile_group && tile_group[tile % m_tiles] < 0) continue;
                 const int acc = local & 1;
                 const uint32_t use = (uint32_t)(local >> 1);
+                ++local;
                 ok = mbar_wait(&acc_empty[acc], (use & 1) ^ 1, p.wait_cycles);    // the epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
@@ -583,9 +603,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     } else {
         const int quarter = warp & 3;
         int local = 0;
-        for (int tile = blockIdx.x; tile < n_total; tile += gridDim.x, ++local) {
+        for (int tile = blockIdx.x; tile < n_total; tile += gridDim.x) {
+            if (tile_group && tile_group[tile % m_tiles] < 0) continue;
             const int acc = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
+            ++local;
             const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], use & 1, p.wait_cycles));
             tc_fence_after();
             if (!ok || *(volatile uint32_t*)abort_flag != 0) {
@@ -610,8 +632,17 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll
                             for (int i = 0; i < 16; ++i) { g[i] += p.bias[f0 + i]; u[i] += p.bias[f0 + 16 + i]; }
                         }
+                        if (p.act_kind == 0) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                            for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const float gg = fminf(g[i], p.act_limit);
+                                const float uu = fminf(fmaxf(u[i], -p.act_limit), p.act_limit);
+                                g[i] = gg / (1.f + expf(-p.act_alpha * gg)) * (uu + 1.f);
+                            }
+                        }
                         OT* dst = row + (f0 >> 1);
                         if (vec_ok) store16(dst, g);
                         else {
@@ -1203,6 +1234,7 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
     p.stages = stages;   // 0: the default of the mode
     p.wait_cycles = g_wait_cycles;
     p.withhold = g_withhold;
+    p.tile_group = nullptr; p.group_rows = 0; p.act_kind = 0; p.act_limit = 0.f; p.act_alpha = 1.f;
     CUtensorMap ma, mb;
     int rc;
     if (swap) {
@@ -1374,4 +1406,47 @@ extern "C" int rb_gemm_tcgen05_qkv_rope(const void* x, const void* w, const floa
                  q_norm_w, k_norm_w, norm_w_f32, norm_eps, cos_sin, nq, nkv};
     return gemm_entry(x, w, bias, nullptr, RB_BF16, M, N, K, ldx, 0, 1, 0, stages, 0, status, stream, 0, nullptr,
                       nullptr, &rope);
+}
+
+
+// Products by tiles of sorted rows on the tensor cores: rows i * 128 .. of x [R, K] (R a multiple of 128) are
+// multiplied with the weight of group tile_group[i], w [groups * N, K] stacked group after group, into the same
+// rows of out [R, N] (bfloat16 or float32); a tile of group -1 is skipped and its rows of out are left as they
+// are.  gated: every group's rows alternate in blocks of 16 between gate and up, out is bfloat16 [R, N / 2] and
+// act_kind chooses the activation (0: silu(g) * u; 1: the clamped one with act_limit and act_alpha).
+// RB_ERR_BAD_SIZE for fewer than 64 features a group, RB_ERR_BAD_ALIGN as rb_gemm_tcgen05.
+extern "C" int rb_gemm_tcgen05_grouped(const void* x, const void* w, void* out, int out_dtype, int R, int N, int K,
+                                       int groups, long long ldx, long long ldo, const int* tile_group, int gated,
+                                       int act_kind, float act_limit, float act_alpha, int* status, void* stream) {
+    if (R <= 0 || N <= 0 || groups <= 0) return RB_OK;
+    if (K <= 0 || R % BM || !tile_group || N <= 64) return RB_ERR_BAD_SIZE;
+    if (K % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return RB_ERR_BAD_ALIGN;
+    if (gated && (out_dtype != RB_BF16 || N % 32)) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int bn = N >= 256 ? 256 : 128;
+    Params p;
+    p.K = K; p.splits = 1; p.ldo = ldo; p.split_stride = 0; p.bias = nullptr; p.status = status; p.stages = 0;
+    p.wait_cycles = g_wait_cycles; p.withhold = 0;
+    p.a_rows = R; p.b_rows = N;
+    p.tile_group = tile_group; p.group_rows = N; p.act_kind = act_kind; p.act_limit = act_limit; p.act_alpha = act_alpha;
+    p.row_sumsq = nullptr; p.row_groups = 0; p.row_sumsq_ld = 0; p.row_eps = 0.f; p.row_inv_width = 0.f;
+    p.resid = nullptr; p.next_w = nullptr; p.xhat = nullptr; p.sumsq = nullptr;
+    p.resid_ld = p.xhat_ld = p.sumsq_ld = 0; p.next_w_f32 = 0;
+    p.q_out = nullptr; p.k_cache = p.v_cache = nullptr; p.positions = p.slot_of_token = p.block_table = nullptr;
+    p.q_norm_w = p.k_norm_w = nullptr; p.cos_sin = nullptr;
+    p.q_ld = 0; p.max_pages = 0; p.norm_w_f32 = 0; p.norm_eps = 0.f; p.nq = p.nkv = 0;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = tensor_map(x, R, K, ldx, BM, &ma)) != RB_OK) return rc;
+    if ((rc = tensor_map(w, (long long)groups * N, K, K, bn, &mb)) != RB_OK) return rc;
+    if (out_dtype == RB_BF16) {
+        if (bn == 256) return gated ? launch_persistent<256, __nv_bfloat16, true>(ma, mb, out, p, s)
+                                    : launch_persistent<256, __nv_bfloat16, false>(ma, mb, out, p, s);
+        return gated ? launch_persistent<128, __nv_bfloat16, true>(ma, mb, out, p, s)
+                     : launch_persistent<128, __nv_bfloat16, false>(ma, mb, out, p, s);
+    }
+    if (out_dtype == RB_F32)
+        return bn == 256 ? launch_persistent<256, float, false>(ma, mb, out, p, s)
+                         : launch_persistent<128, float, false>(ma, mb, out, p, s);
+    return RB_ERR_BAD_DTYPE;
 }

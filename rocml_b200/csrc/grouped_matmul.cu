@@ -7,7 +7,7 @@
 //     (optional, float32 [M, groups]) multiplies group g's result for row m.
 //   * tiles: x holds rows sorted by group, each group's rows starting at a multiple of `tile_rows`;
 //     tile_group[i] names the group of rows i * tile_rows .. (-1: an unused tile).  Used for routed
-//     experts.  tile_rows must equal the kernel's row tile (16 or 64).
+//     experts.  tile_rows is 16 (the kernels' small row tile) or a multiple of 64 (their large one).
 // W is [groups][N][K], K contiguous.  Accumulation is 32-bit with k ascending, so a row's result depends on
 // nothing but the row and the weight.  bfloat16 operands whose rows start on 16 bytes take the tensor cores
 // (mma.sync m16n8k16, operands through padded shared-memory tiles filled by cp.async, two stages); everything
@@ -44,7 +44,7 @@ grouped_fma_kernel(const GP p) {
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     int m_end = p.M;
     if (p.tile_group) {
-        g = p.tile_group[blockIdx.y];
+        g = p.tile_group[m0 / p.tile_rows];
         if (g < 0) return;
         m_end = m0 + BM;
     }
@@ -113,7 +113,7 @@ grouped_mma_kernel(const GP p) {
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     int m_end = p.M;
     if (p.tile_group) {
-        g = p.tile_group[blockIdx.y];
+        g = p.tile_group[m0 / p.tile_rows];
         if (g < 0) return;
         m_end = m0 + BM;
     }
@@ -231,14 +231,14 @@ int launch_mma(const GP& p, int groups, int row_tiles, bool small, cudaStream_t 
 }  // namespace
 
 // groups > 0, tile_group absent: the heads form (M rows).  tile_group given: the tiles form; M is then the
-// number of rows the buffers hold (n_tiles * tile_rows) and tile_rows is 16 or 64.
+// number of rows the buffers hold (n_tiles * tile_rows) and tile_rows is 16 or a multiple of 64.
 extern "C" int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int x_col_stride, const void* w, int w_dtype,
                                  long long w_group_stride, void* out, int out_dtype, long long ldo, int o_col_stride,
                                  int M, int N, int K, int groups, const int* tile_group, int tile_rows,
                                  const float* row_scale, int row_scale_ld, void* stream) {
     if (M <= 0 || N <= 0 || groups <= 0) return RB_OK;
     if (K <= 0) return RB_ERR_BAD_SIZE;
-    if (tile_group && tile_rows != 16 && tile_rows != 64) return RB_ERR_BAD_SIZE;
+    if (tile_group && tile_rows != 16 && (tile_rows <= 0 || tile_rows % 64)) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     GP p;
     p.x = x; p.ldx = ldx; p.x_col_stride = x_col_stride;
@@ -249,7 +249,7 @@ extern "C" int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int 
     p.row_scale = row_scale; p.row_scale_ld = row_scale_ld;
     const bool small = tile_group ? tile_rows == 16 : M <= 16;
     const int bm = small ? 16 : 64;
-    const long long row_tiles = tile_group ? M / tile_rows : (M + bm - 1) / bm;
+    const long long row_tiles = tile_group ? M / bm : (M + bm - 1) / bm;
     const int z = tile_group ? 1 : groups;
     if (row_tiles > 65535 || z > 65535) return RB_ERR_BAD_SIZE;
     typedef __nv_bfloat16 bf;

@@ -17,6 +17,82 @@ using namespace rb;
 namespace {
 constexpr int MAX_EPL = 16;   // experts per lane: up to 512 experts
 
+// ---- router logits: z[t, e] = sum_k x[t, k] * w[e, k], 32-bit FMA, w float32 ---------------------------------
+// A block takes TT tokens (their rows staged in shared memory as float32) and 8 experts, a warp one expert: its
+// lanes stream the expert's row with 16-byte loads, every lane multiplying its slice of k with the same slice of
+// the block's tokens, and the lanes' sums meet in a shuffle tree.  How k is dealt out depends on K only, so a
+// token's logits depend on nothing else in the batch.
+constexpr int RT_WARPS = 8;
+
+template <typename XT, int TT>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+router_logits_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ w, float* __restrict__ z, int ldz,
+                     int T, int E, int K) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float xs[];      // [TT][K]
+    const int t0 = blockIdx.x * TT;
+    for (int idx = threadIdx.x; idx < TT * K; idx += blockDim.x) {
+        const int r = idx / K, k = idx - r * K;
+        xs[idx] = t0 + r < T ? to_f32(x[(size_t)(t0 + r) * ldx + k]) : 0.f;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * RT_WARPS + warp;
+    if (e >= E) return;
+    const float* row = w + (size_t)e * K;
+    float acc[TT];
+#pragma unroll
+    for (int r = 0; r < TT; ++r) acc[r] = 0.f;
+    if ((K & 3) == 0 && ((uintptr_t)w & 15) == 0) {
+        const int K4 = K >> 2;
+        for (int k4 = lane; k4 < K4; k4 += 32 * 4) {           // four 16-byte loads in flight a lane
+            float4 wv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                wv[u] = k4 + u * 32 < K4 ? reinterpret_cast<const float4*>(row)[k4 + u * 32] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (k4 + u * 32 >= K4) continue;
+#pragma unroll
+                for (int r = 0; r < TT; ++r) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xs + (size_t)r * K + (size_t)(k4 + u * 32) * 4);
+                    acc[r] = fmaf(wv[u].x, xv.x, acc[r]);
+                    acc[r] = fmaf(wv[u].y, xv.y, acc[r]);
+                    acc[r] = fmaf(wv[u].z, xv.z, acc[r]);
+                    acc[r] = fmaf(wv[u].w, xv.w, acc[r]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = row[k];
+#pragma unroll
+            for (int r = 0; r < TT; ++r) acc[r] = fmaf(wv, xs[(size_t)r * K + k], acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < TT; ++r) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && t0 + r < T) z[(size_t)(t0 + r) * ldz + e] = v;
+    }
+}
+
+template <typename XT, int TT>
+int launch_router(const void* x, long long ldx, const float* w, float* z, int ldz, int T, int E, int K, cudaStream_t s) {
+    const size_t smem = (size_t)TT * K * sizeof(float);
+    auto k = router_logits_kernel<XT, TT>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid((T + TT - 1) / TT, (E + RT_WARPS - 1) / RT_WARPS);
+    if (grid.y > 65535) return RB_ERR_BAD_SIZE;
+    RB_LAUNCH((k), grid, dim3(RT_WARPS * 32), smem, s, (const XT*)x, ldx, w, z, ldz, T, E, K);
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
 template <typename BT>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int ldz, const BT* __restrict__ bias, const int* __restrict__ slot_of_token,
@@ -130,6 +206,28 @@ moe_combine_kernel(const float* __restrict__ y, long long ldy, const int* __rest
     }
 }
 }  // namespace
+
+extern "C" int rb_router_logits(const void* x, int x_dtype, long long ldx, const float* w, float* z, int ldz, int T, int E,
+                                int K, void* stream) {
+    if (T <= 0 || E <= 0) return RB_OK;
+    if (K <= 0) return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    // tokens a block: as many as fit 96 KB of shared memory, at most 8
+    const int fit = (int)((96 * 1024) / ((size_t)K * sizeof(float)));
+    if (fit < 1) return RB_ERR_BAD_SIZE;
+    const int tt = fit >= 8 ? 8 : (fit >= 4 ? 4 : (fit >= 2 ? 2 : 1));
+#define RB_RL(XT)                                                                         \
+    switch (tt) {                                                                         \
+        case 8: return launch_router<XT, 8>(x, ldx, w, z, ldz, T, E, K, s);               \
+        case 4: return launch_router<XT, 4>(x, ldx, w, z, ldz, T, E, K, s);               \
+        case 2: return launch_router<XT, 2>(x, ldx, w, z, ldz, T, E, K, s);               \
+        default: return launch_router<XT, 1>(x, ldx, w, z, ldz, T, E, K, s);              \
+    }
+    if (x_dtype == RB_BF16) { RB_RL(__nv_bfloat16) }
+    if (x_dtype == RB_F32) { RB_RL(float) }
+#undef RB_RL
+    return RB_ERR_BAD_DTYPE;
+}
 
 extern "C" int rb_moe_route(const float* z, int ldz, const void* bias, int bias_dtype, const int* slot_of_token, int T,
                             int E, int top, int* ids, float* weights, int* place, int* counts, void* stream) {

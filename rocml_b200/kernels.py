@@ -158,7 +158,9 @@ def _lib():
         lib.rb_embedding_pos.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp]
         lib.rb_residual_inject.argtypes = [_vp, _vp, _i, _ll, _vp, _vp, _i, _i, _i, _vp]
         lib.rb_postnorm_add_norm.argtypes = [_vp, _vp, _i, _ll, _vp, _f, _vp, _f, _i, _vp, _i, _i, _i, _vp]
-        lib.rb_gated_act.argtypes = [_vp, _i, _i, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _f, _f, _vp]
+        lib.rb_gated_act.argtypes = [_vp, _i, _i, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _f, _f, _i, _vp]
+        lib.rb_router_logits.argtypes = [_vp, _i, _ll, _vp, _vp, _i, _i, _i, _i, _vp]
+        lib.rb_gemm_tcgen05_grouped.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _i, _i, _f, _f, _vp, _vp]
         lib.rb_scale.argtypes = [_vp, _ll, _f, _vp]
         lib.rb_latent_prep.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _vp, _i, _f, _vp, _i, _vp, _vp, _i, _vp, _vp,
                                        _vp, _i, _i, _vp]
@@ -910,10 +912,10 @@ GATED_ACTS = {"silu": 0, "clamped_swish": 1}
 @_profiled(lambda a, facts: _cost.silu_mul(a["out"].shape[0] if a["rows"] is None else a["rows"], a["out"].shape[1],
                                            _n_in(a["x"]), _esz(a["x"]), _esz(a["out"])))
 def gated_act(x: torch.Tensor, out: torch.Tensor, kind: str = "silu", limit: float = 0.0, alpha: float = 1.0,
-              rows: Optional[int] = None):
+              rows: Optional[int] = None, paired: bool = False):
     """x [R, 2I] = [gate | up] (or [S, R, 2I] partial sums, added first) -> out [R, I].  ``kind`` "silu":
     silu(gate) * up; "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit),
-    g * sigmoid(alpha * g) * (u + 1)."""
+    g * sigmoid(alpha * g) * (u + 1).  ``paired``: gates and ups alternate in blocks of 16 columns."""
     if kind not in GATED_ACTS:
         raise KernelError(f"gated_act: unknown kind {kind!r} (known: {sorted(GATED_ACTS)})")
     n_in, in_stride, row_stride = _partials(x, "gated_act")
@@ -922,7 +924,8 @@ def gated_act(x: torch.Tensor, out: torch.Tensor, kind: str = "silu", limit: flo
     if I2 % 2 or out.shape[-1] != I2 // 2 or out.stride(-1) != 1 or out.shape[0] < n or n > R:
         raise KernelError("gated_act: shapes do not fit")
     _check(_lib().rb_gated_act(_ptr(x), dtype_code(x.dtype), n_in, in_stride, row_stride, _ptr(out), dtype_code(out.dtype),
-                               out.stride(0), n, I2 // 2, GATED_ACTS[kind], float(limit), float(alpha), _stream()),
+                               out.stride(0), n, I2 // 2, GATED_ACTS[kind], float(limit), float(alpha),
+                               1 if paired else 0, _stream()),
            "gated_act")
 
 
@@ -967,6 +970,17 @@ def latent_prep(proj: torch.Tensor, n_tokens: int, q_width: int, rank: int, n_ga
 
 
 # ---- routed experts -----------------------------------------------------------------------------------------------
+
+@_profiled(lambda a, facts: _cost.linear(a["n_tokens"], a["w"].shape[0], a["w"].shape[1], 4, _esz(a["x"]), 4))
+def router_logits(x: torch.Tensor, w: torch.Tensor, z: torch.Tensor, n_tokens: int):
+    """z [T, E] float32 = x [T, K] . w [E, K]^T with 32-bit FMA; w float32, x bfloat16 or float32."""
+    E, K = w.shape
+    if w.dtype != torch.float32 or not w.is_contiguous() or z.dtype != torch.float32 or z.stride(1) != 1 or \
+            z.shape[1] != E or x.shape[1] != K or x.stride(1) != 1 or x.shape[0] < n_tokens or z.shape[0] < n_tokens:
+        raise KernelError("router_logits: w must be contiguous float32 [E, K], z float32 [T, E], x [T, K]")
+    _check(_lib().rb_router_logits(_ptr(x), dtype_code(x.dtype), x.stride(0), _ptr(w), _ptr(z), z.stride(0), n_tokens, E, K,
+                                   _stream()), "router_logits")
+
 
 @_profiled(lambda a, facts: (a["n_tokens"] * (a["z"].shape[1] * 4 + a["top"] * 12), a["n_tokens"] * a["z"].shape[1] * 8))
 def moe_route(z: torch.Tensor, bias: Optional[torch.Tensor], slot_of_token: torch.Tensor, n_tokens: int, top: int,
@@ -1056,3 +1070,30 @@ def tile_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group:
                                   _ptr(out), dtype_code(out.dtype), out.stride(0), 0, R, N, K, G,
                                   _i32(tile_group, "tile_group"), int(tile_rows), None, 0, _stream())
     _check(rc, "tile_matmul")
+
+
+@_profiled(lambda a, facts: ((a["w"].numel() * 2 + a["x"].shape[0] * (a["w"].shape[2] * 2 + a["out"].shape[1] * _esz(a["out"])),
+                              2 * a["x"].shape[0] * a["w"].shape[1] * a["w"].shape[2])))
+def tile_matmul_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, act: Optional[str] = None,
+                    limit: float = 0.0, alpha: float = 1.0) -> bool:
+    """``tile_matmul`` for tiles of 128 rows on the tcgen05 tensor cores (the persistent product, each row tile
+    taking its group's weight): x bfloat16 [R, K], w bfloat16 [G, N, K], out bfloat16 or float32 [R, N].  With
+    ``act`` every group's rows of w alternate in blocks of 16 between gate and up, and out is bfloat16 [R, N / 2]
+    = the gated activation (see ``gated_act``).  Returns False when the kernel refuses the sizes or the alignment."""
+    G, N, K = w.shape
+    R = x.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() or \
+            x.shape[1] != K or out.stride(1) != 1 or out.shape[0] != R or out.shape[1] != (N // 2 if act else N):
+        raise KernelError("tile_matmul_tc5: x and w must be bfloat16, K-major, out [R, N] (or [R, N / 2] when gated)")
+    if R % 128 or tile_group.numel() < R // 128:
+        raise KernelError("tile_matmul_tc5: rows must come in tiles of 128, each with its group")
+    if act is not None and act not in GATED_ACTS:
+        raise KernelError(f"tile_matmul_tc5: unknown activation {act!r}")
+    rc = _lib().rb_gemm_tcgen05_grouped(_ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), R, N, K, G, x.stride(0),
+                                        out.stride(0), _i32(tile_group, "tile_group"), 1 if act else 0,
+                                        GATED_ACTS.get(act, 0), float(limit), float(alpha), _ptr(status_word(x.device)),
+                                        _stream())
+    if rc in (10001, 10003):
+        return False
+    _check(rc, "tile_matmul_tc5")
+    return True

@@ -12,7 +12,10 @@ How a step runs, without the host ever learning who chose what (so a decode step
 the router's product, one kernel that scores, chooses and counts, one that lays every expert's rows out
 from a multiple of the row tile, one that copies each token's row to its places, two products over
 tiles of those rows (every tile names its expert's weight), the activation between them, and a
-weighted sum back into token order.  The row tile is 16 for few tokens and 64 beyond.
+weighted sum back into token order.  The row tile is 16 for few tokens and 64 beyond (mma.sync, or FMA in
+32-bit); from a thousand token-choices in bfloat16 it is 128 and the two products are the persistent tcgen05
+product, the first with the activation in its epilogue (the experts' gate and up rows are interleaved in
+blocks of 16 at load time for that).
 """
 from __future__ import annotations
 
@@ -30,8 +33,9 @@ from .base import BuildEnv, FeedForward, register_feed_forward
 TENSOR_NAMES = {"router": "gate", "choice_bias": "e_score_correction_bias", "expert": "experts.{e}.", "gate": "gate_proj",
                 "up": "up_proj", "down": "down_proj"}
 
-SMALL_TILE, LARGE_TILE = 16, 64
+SMALL_TILE, LARGE_TILE, TENSOR_TILE = 16, 64, 128
 SMALL_TILE_MAX_ROWS = 256      # token-choices up to which the 16-row tile is used
+TENSOR_TILE_MIN_ROWS = 1024    # token-choices from which tiles of 128 rows go to the tcgen05 product
 
 
 @register_feed_forward("routed_mlp")
@@ -68,6 +72,7 @@ class RoutedMLP(FeedForward):
         self.choice_bias: Optional[torch.Tensor] = None    # float32 [experts]
         self.gate_up: Optional[torch.Tensor] = None        # [experts, 2 * inter, hidden]: gate rows, then up rows
         self.down: Optional[torch.Tensor] = None           # [experts, hidden, inter]
+        self.paired = False                                # gate and up rows alternate in blocks of 16 instead
 
     def _expert(self, prefix: str, e: int, role: str) -> str:
         return f"{prefix}{self.names['expert'].format(e=e)}{self.names[role]}.weight"
@@ -89,6 +94,11 @@ class RoutedMLP(FeedForward):
         gu = [torch.cat([tensors[self._expert(prefix, e, "gate")], tensors[self._expert(prefix, e, "up")]], dim=0)
               for e in range(self.experts)]
         self.gate_up = torch.stack(gu).contiguous()
+        if self.gate_up.dtype == torch.bfloat16 and self.inter % 16 == 0:
+            g, u = self.gate_up[:, :self.inter], self.gate_up[:, self.inter:]
+            shape = (self.experts, self.inter // 16, 16, self.hidden)
+            self.gate_up = torch.stack([g.reshape(shape), u.reshape(shape)], dim=2).reshape(self.gate_up.shape).contiguous()
+            self.paired = True
         self.down = torch.stack([tensors[self._expert(prefix, e, "down")] for e in range(self.experts)]).contiguous()
 
     def weight_bytes(self) -> int:
@@ -96,7 +106,15 @@ class RoutedMLP(FeedForward):
         esz = 4 if self.env.mode == "float32" else 2
         return self.experts * self.hidden * 4 + self.experts * 3 * self.inter * self.hidden * esz
 
+    def _tensor_tiles(self, n_tokens: int) -> bool:
+        """Whether this step's products take the tcgen05 kernel: bfloat16, enough rows, sizes it addresses."""
+        return (self.paired and self.env.act_dtype == torch.bfloat16 and n_tokens * self.top >= TENSOR_TILE_MIN_ROWS
+                and self.hidden % 8 == 0 and self.inter % 16 == 0 and self.inter > 32 and self.hidden > 64
+                and self.gate_up is not None and self.gate_up.is_cuda)
+
     def _tile(self, n_tokens: int) -> int:
+        if self._tensor_tiles(n_tokens):
+            return TENSOR_TILE
         return SMALL_TILE if n_tokens * self.top <= SMALL_TILE_MAX_ROWS else LARGE_TILE
 
     def _max_tiles(self, n_tokens: int) -> int:
@@ -125,7 +143,7 @@ class RoutedMLP(FeedForward):
         rows = max_tiles * tile
         z = torch.empty((T, E), dtype=torch.float32, device=dev)
         with scope(op="router"):
-            kernels.gemm_generic(xn, self.router, z, None, T)
+            kernels.router_logits(xn, self.router, z, T)
         ids = torch.empty((T, top), dtype=torch.int32, device=dev)
         place = torch.empty((T, top), dtype=torch.int32, device=dev)
         weights = torch.empty((T, top), dtype=torch.float32, device=dev)
@@ -138,15 +156,21 @@ class RoutedMLP(FeedForward):
             kernels.moe_plan(counts, tile, starts, tile_group)
             xs = torch.empty((rows, self.hidden), dtype=act, device=dev)
             kernels.moe_gather(xn, ids, place, starts, T, top, xs, row_of)
-        gu = torch.empty((rows, 2 * self.inter), dtype=act, device=dev)
-        with scope(op="experts_gate_up"):
-            kernels.tile_matmul(xs, self.gate_up, gu, tile_group, tile)
         y = torch.empty((rows, self.inter), dtype=act, device=dev)
-        with scope(op="experts_act"):
-            kernels.gated_act(gu, y, self.act, self.limit, self.alpha)
+        fused = False
+        if tile == TENSOR_TILE:
+            with scope(op="experts_gate_up"):
+                fused = kernels.tile_matmul_tc5(xs, self.gate_up, y, tile_group, self.act, self.limit, self.alpha)
+        if not fused:
+            gu = torch.empty((rows, 2 * self.inter), dtype=act, device=dev)
+            with scope(op="experts_gate_up"):
+                kernels.tile_matmul(xs, self.gate_up, gu, tile_group, tile)
+            with scope(op="experts_act"):
+                kernels.gated_act(gu, y, self.act, self.limit, self.alpha, paired=self.paired)
         out_rows = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         with scope(op="experts_down"):
-            kernels.tile_matmul(y, self.down, out_rows, tile_group, tile)
+            if not (tile == TENSOR_TILE and kernels.tile_matmul_tc5(y, self.down, out_rows, tile_group)):
+                kernels.tile_matmul(y, self.down, out_rows, tile_group, tile)
         delta = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
         with scope(op="experts_sum"):
             kernels.moe_combine(out_rows, row_of, weights, T, top, delta[0])

@@ -135,6 +135,19 @@ def test_products_head_by_head(dtype, G, N, K, T):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T, E, K", [(1, 3, 20), (8, 32, 256), (13, 7, 72), (70, 64, 1024), (5, 9, 5000)])
+def test_router_logits_are_32_bit(dtype, T, E, K):
+    from rocml_b200 import kernels
+    dev = torch.device("cuda:0")
+    torch.manual_seed(T + E + K)
+    x = torch.randn(T + 2, K + 3).to(DT[dtype])[:, :K]            # rows with a stride of their own
+    w = torch.randn(E, K)
+    z = torch.full((T, E), 9.0, dtype=torch.float32, device=dev)
+    kernels.router_logits(x.to(dev), w.to(dev), z, T)
+    assert close(z, x[:T].double() @ w.double().t(), 2e-6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_latent_norm_into_the_cache_and_gates(dtype):
     from rocml_b200 import kernels
     dev = torch.device("cuda:0")
@@ -162,10 +175,12 @@ def test_latent_norm_into_the_cache_and_gates(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T, E, top, D, F", [(5, 3, 3, 24, 20), (40, 7, 2, 64, 48), (300, 16, 1, 32, 16), (130, 5, 4, 40, 12)])
+@pytest.mark.parametrize("T, E, top, D, F", [(5, 3, 3, 24, 20), (40, 7, 2, 64, 48), (300, 16, 1, 32, 16), (130, 5, 4, 40, 12),
+                                             (300, 16, 4, 128, 64), (600, 4, 2, 256, 160), (1100, 9, 1, 72, 48)])
 def test_routed_feed_forward_alone(dtype, T, E, top, D, F):
     """The routed part by itself: choices, weights and the weighted sum of the chosen experts; padding tokens
-    (slot -1) get zeros."""
+    (slot -1) get zeros.  Row tiles of 16, 64 and (the last three cases in bfloat16) 128 on the tcgen05 product,
+    with feature tiles of 128 and 256, an expert without rows, and sizes that are no multiple of a tile."""
     from rocml_b200.config.specs import FeedForwardSpec
     from rocml_b200.parts import BuildEnv, build_feed_forward
     dev = torch.device("cuda:0")
