@@ -25,10 +25,12 @@ int rb_embedding_pos(const int* ids, const void* table, int table_dtype, float* 
 int rb_residual_inject(float* resid, const float* delta, int n_delta, long long delta_stride, const float* other,
                        const void* vec, int vec_dtype, int T, int H, void* stream);
 
-// resid += rmsnorm(sum of delta) * w_post; out = rmsnorm(resid) * w_next when w_next is given.
-int rb_postnorm_add_norm(float* resid, const float* delta, int n_delta, long long delta_stride, const void* w_post,
-                         float eps_post, const void* w_next, float eps_next, int w_dtype, void* out, int out_dtype,
-                         int n_rows, int H, void* stream);
+// resid += rmsnorm(d) * w_post; out = rmsnorm(resid) * w_next when w_next is given.  d is the sum of the delta
+// partial sums, or, with row_of, the weighted sum of a token's rows of delta: sum_j weights[t, j] *
+// delta[row_of[t, j]] (delta_stride is then the row stride, top the choices a token).
+int rb_postnorm_add_norm(float* resid, const float* delta, int n_delta, long long delta_stride, const int* row_of,
+                         const float* weights, int top, const void* w_post, float eps_post, const void* w_next,
+                         float eps_next, int w_dtype, void* out, int out_dtype, int n_rows, int H, void* stream);
 
 // [gate | up] halves -> out; kind 0: silu(g) * u; kind 1: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u) + 1).
 // paired: gates and ups alternate in blocks of 16 columns instead of lying in two halves.
@@ -59,7 +61,7 @@ int rb_moe_combine(const float* y, long long ldy, const int* row_of, const float
 int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int x_col_stride, const void* w, int w_dtype,
                       long long w_group_stride, void* out, int out_dtype, long long ldo, int o_col_stride, int M, int N,
                       int K, int groups, const int* tile_group, int tile_rows, const float* row_scale, int row_scale_ld,
-                      void* stream);
+                      int act, float limit, float alpha, void* stream);
 
 // Keeps the stream busy for about that long (at most a second): the profiler's gate.
 int rb_hold(long long microseconds, void* stream);

@@ -457,12 +457,16 @@ extern "C" int rb_residual_inject(float* resid, const float* delta, int n_delta,
 }
 
 // ---- a norm on a sublayer's output, the addition, and the next sublayer's norm --------------------------
-// d = sum_s delta[s][row]  (s in order);  resid[row] += d * rsqrt(mean(d^2) + eps_post) * w_post;
+// d = sum_s delta[s][row]  (s in order), or, with row_of, sum_j weights[row, j] * delta[row_of[row, j]] (j in order: a
+// routed feed-forward's rows, summed here instead of in a kernel of their own);
+// resid[row] += d * rsqrt(mean(d^2) + eps_post) * w_post;
 // if w_next: out[row] = resid[row] * rsqrt(mean(resid[row]^2) + eps_next) * w_next.
 // One block a row; the row stays in shared memory between the passes.  All arithmetic is 32-bit.
 template <typename OT, typename WT>
 __global__ void __launch_bounds__(1024) postnorm_add_norm_kernel(float* __restrict__ resid, const float* __restrict__ delta,
                                                                  int n_delta, size_t delta_stride,
+                                                                 const int* __restrict__ row_of,
+                                                                 const float* __restrict__ weights, int top,
                                                                  const WT* __restrict__ w_post, float eps_post,
                                                                  const WT* __restrict__ w_next, float eps_next,
                                                                  OT* __restrict__ out, int H) {
@@ -473,11 +477,23 @@ __global__ void __launch_bounds__(1024) postnorm_add_norm_kernel(float* __restri
     const int row = blockIdx.x;
     float* r = resid + (size_t)row * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = 0.f;
-        for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + (size_t)row * H + i];
-        row_buf[i] = v;
-        ss += v * v;
+    if (row_of) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = 0.f;
+            for (int j = 0; j < top; ++j) {
+                const int src = row_of[(size_t)row * top + j];
+                if (src >= 0) v = fmaf(weights[(size_t)row * top + j], delta[(size_t)src * delta_stride + i], v);
+            }
+            row_buf[i] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = 0.f;
+            for (int s = 0; s < n_delta; ++s) v += delta[(size_t)s * delta_stride + (size_t)row * H + i];
+            row_buf[i] = v;
+            ss += v * v;
+        }
     }
     const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps_post);
     float ss2 = 0.f;
@@ -494,7 +510,8 @@ __global__ void __launch_bounds__(1024) postnorm_add_norm_kernel(float* __restri
 }
 
 template <typename OT, typename WT>
-static int launch_postnorm(float* resid, const float* delta, int n_delta, size_t delta_stride, const void* w_post,
+static int launch_postnorm(float* resid, const float* delta, int n_delta, size_t delta_stride, const int* row_of,
+                           const float* weights, int top, const void* w_post,
                            float eps_post, const void* w_next, float eps_next, void* out, int n_rows, int H,
                            cudaStream_t s) {
     const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
@@ -505,27 +522,28 @@ static int launch_postnorm(float* resid, const float* delta, int n_delta, size_t
         if (e != cudaSuccess) return (int)e;
     }
     const int threads = H >= 4096 ? 1024 : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
-    RB_LAUNCH((k), dim3(n_rows), dim3(threads), smem, s, resid, delta, n_delta, delta_stride, (const WT*)w_post, eps_post,
-              (const WT*)w_next, eps_next, (OT*)out, H);
+    RB_LAUNCH((k), dim3(n_rows), dim3(threads), smem, s, resid, delta, n_delta, delta_stride, row_of, weights, top,
+              (const WT*)w_post, eps_post, (const WT*)w_next, eps_next, (OT*)out, H);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }
 
 extern "C" int rb_postnorm_add_norm(float* resid, const float* delta, int n_delta, long long delta_stride,
+                                    const int* row_of, const float* weights, int top,
                                     const void* w_post, float eps_post, const void* w_next, float eps_next, int w_dtype,
                                     void* out, int out_dtype, int n_rows, int H, void* stream) {
     if (n_rows <= 0) return RB_OK;
-    if (n_delta < 1 || !delta || !w_post) return RB_ERR_BAD_SIZE;
+    if (n_delta < 1 || !delta || !w_post || (row_of && (!weights || top < 1))) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t ds = (size_t)delta_stride;
     if (out_dtype == RB_BF16 && w_dtype == RB_BF16)
-        return launch_postnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+        return launch_postnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_delta, ds, row_of, weights, top, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
     if (out_dtype == RB_BF16 && w_dtype == RB_F32)
-        return launch_postnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+        return launch_postnorm<__nv_bfloat16, float>(resid, delta, n_delta, ds, row_of, weights, top, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
     if (out_dtype == RB_F32 && w_dtype == RB_BF16)
-        return launch_postnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+        return launch_postnorm<float, __nv_bfloat16>(resid, delta, n_delta, ds, row_of, weights, top, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
     if (out_dtype == RB_F32 && w_dtype == RB_F32)
-        return launch_postnorm<float, float>(resid, delta, n_delta, ds, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
+        return launch_postnorm<float, float>(resid, delta, n_delta, ds, row_of, weights, top, w_post, eps_post, w_next, eps_next, out, n_rows, H, s);
     return RB_ERR_BAD_DTYPE;
 }
 

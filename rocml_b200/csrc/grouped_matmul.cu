@@ -28,6 +28,9 @@ struct GP {
     int M, N, K;
     const int* tile_group; int tile_rows;
     const float* row_scale; int row_scale_ld;
+    // tensor-core kernel only: W's rows alternate in blocks of 16 between gate and up; out gets N / 2 columns,
+    // act 1: silu(g) * u, act 2: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)
+    int act; float limit, alpha;
 };
 
 // ---- CUDA cores -------------------------------------------------------------------------------------
@@ -176,6 +179,36 @@ grouped_mma_kernel(const GP p) {
         __syncthreads();
     }
     OT* out = (OT*)p.out + (size_t)g * p.o_col_stride;
+    if (p.act != 0) {
+        // a warp's 32 columns are 16 gates and the 16 ups of the same outputs: tiles 0, 1 and tiles 2, 3
+        static_assert(NT == 4, "the gated epilogue pairs tiles 0, 1 with tiles 2, 3");
+        const int half = p.N >> 1;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int m = m0 + (wm * MT + i) * 16 + (lane >> 2) + h * 8;
+                if (m >= m_end) continue;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int f = ((n0 + wn * NT * 8) >> 1) + j * 8 + (lane & 3) * 2;
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        float gg = acc[i][j][h * 2 + c], uu = acc[i][j + 2][h * 2 + c], v;
+                        if (p.act == 1) {
+                            v = gg / (1.f + expf(-gg)) * uu;
+                        } else {
+                            gg = fminf(gg, p.limit);
+                            uu = fminf(fmaxf(uu, -p.limit), p.limit);
+                            v = gg / (1.f + expf(-p.alpha * gg)) * (uu + 1.f);
+                        }
+                        if (f + c < half) out[(size_t)m * p.ldo + f + c] = from_f32<OT>(v);
+                    }
+                }
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
 #pragma unroll
@@ -218,6 +251,13 @@ int launch_fma(const GP& p, int groups, int row_tiles, bool small, cudaStream_t 
 
 template <typename OT>
 int launch_mma(const GP& p, int groups, int row_tiles, bool small, cudaStream_t s) {
+    if (!small && !p.tile_group && p.M >= 512 && p.N >= 128) {
+        // many rows, head by head: tiles of 128 x 128, eight warps of 64 x 32
+        dim3 grid((p.N + 127) / 128, (p.M + 127) / 128, groups);
+        RB_LAUNCH((grouped_mma_kernel<OT, 2, 4, 4, 4>), grid, dim3(256), 0, s, p);
+        RB_LAUNCH_CHECK();
+        return RB_OK;
+    }
     if (small) {
         dim3 grid((p.N + 127) / 128, row_tiles, groups);
         RB_LAUNCH((grouped_mma_kernel<OT, 1, 4, 1, 4>), grid, dim3(128), 0, s, p);
@@ -230,12 +270,16 @@ int launch_mma(const GP& p, int groups, int row_tiles, bool small, cudaStream_t 
 }
 }  // namespace
 
+// act != 0 (bfloat16 operands on the tensor cores only, N a multiple of 32, W's gate and up rows interleaved in
+// blocks of 16): out has N / 2 columns, the gated activation of the product; RB_ERR_BAD_SIZE when the operands take
+// the FMA kernel, which has no such epilogue.
 // groups > 0, tile_group absent: the heads form (M rows).  tile_group given: the tiles form; M is then the
 // number of rows the buffers hold (n_tiles * tile_rows) and tile_rows is 16 or a multiple of 64.
 extern "C" int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int x_col_stride, const void* w, int w_dtype,
                                  long long w_group_stride, void* out, int out_dtype, long long ldo, int o_col_stride,
                                  int M, int N, int K, int groups, const int* tile_group, int tile_rows,
-                                 const float* row_scale, int row_scale_ld, void* stream) {
+                                 const float* row_scale, int row_scale_ld, int act, float limit, float alpha,
+                                 void* stream) {
     if (M <= 0 || N <= 0 || groups <= 0) return RB_OK;
     if (K <= 0) return RB_ERR_BAD_SIZE;
     if (tile_group && tile_rows != 16 && (tile_rows <= 0 || tile_rows % 64)) return RB_ERR_BAD_SIZE;
@@ -247,6 +291,7 @@ extern "C" int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int 
     p.M = M; p.N = N; p.K = K;
     p.tile_group = tile_group; p.tile_rows = tile_rows;
     p.row_scale = row_scale; p.row_scale_ld = row_scale_ld;
+    p.act = act; p.limit = limit; p.alpha = alpha;
     const bool small = tile_group ? tile_rows == 16 : M <= 16;
     const int bm = small ? 16 : 64;
     const long long row_tiles = tile_group ? M / bm : (M + bm - 1) / bm;
@@ -255,10 +300,12 @@ extern "C" int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int 
     typedef __nv_bfloat16 bf;
     if (x_dtype == RB_BF16 && w_dtype == RB_BF16 && mma_enabled() && K % 8 == 0 && ldx % 8 == 0 && x_col_stride % 8 == 0 &&
         w_group_stride % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+        if (act != 0 && (N % 32 || act > 2 || row_scale)) return RB_ERR_BAD_SIZE;
         if (out_dtype == RB_BF16) return launch_mma<bf>(p, z, (int)row_tiles, small, s);
         if (out_dtype == RB_F32) return launch_mma<float>(p, z, (int)row_tiles, small, s);
         return RB_ERR_BAD_DTYPE;
     }
+    if (act != 0) return RB_ERR_BAD_SIZE;       // only the tensor-core kernel has the gated epilogue
 #define RB_GF(XT, WT, OT) return launch_fma<XT, WT, OT>(p, z, (int)row_tiles, small, s)
     if (x_dtype == RB_F32 && w_dtype == RB_F32 && out_dtype == RB_F32) RB_GF(float, float, float);
     if (x_dtype == RB_BF16 && w_dtype == RB_BF16 && out_dtype == RB_BF16) RB_GF(bf, bf, bf);

@@ -16,8 +16,22 @@
 using namespace rb;
 
 namespace {
+// The sum of up to n_in partial sums `stride` apart, in their order, eight loads in flight at a time.
+template <typename IT>
+__device__ __forceinline__ float sum_parts(const IT* p, size_t stride, int n_in) {
+    float v = 0.f;
+    for (int s0 = 0; s0 < n_in; s0 += 8) {
+        float d[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d[j] = s0 + j < n_in ? to_f32(p[(size_t)(s0 + j) * stride]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v += d[j];
+    }
+    return v;
+}
+
 template <typename IT, typename AT, typename WT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_prep_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int q_width, int rank, int n_gate,
                    const WT* __restrict__ w, float eps, AT* __restrict__ q_out, int q_stride, float* __restrict__ gate_out,
                    AT* __restrict__ cache, const int* __restrict__ positions, const int* __restrict__ slot_of_token,
@@ -32,8 +46,7 @@ latent_prep_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int ro
     const IT* row = in + (size_t)t * row_stride;
     float ss = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) {
-        float v = 0.f;
-        for (int s = 0; s < n_in; ++s) v += to_f32(row[(size_t)s * in_stride + q_width + i]);
+        const float v = sum_parts(row + q_width + i, in_stride, n_in);
         buf[i] = v;
         ss += v * v;
     }
@@ -46,14 +59,11 @@ latent_prep_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int ro
     }
     if (q_out) {
         for (int i = threadIdx.x; i < q_width; i += blockDim.x) {
-            float v = 0.f;
-            for (int s = 0; s < n_in; ++s) v += to_f32(row[(size_t)s * in_stride + i]);
-            q_out[(size_t)t * q_stride + i] = from_f32<AT>(v);
+            q_out[(size_t)t * q_stride + i] = from_f32<AT>(sum_parts(row + i, in_stride, n_in));
         }
     }
     for (int i = threadIdx.x; i < n_gate; i += blockDim.x) {
-        float v = 0.f;
-        for (int s = 0; s < n_in; ++s) v += to_f32(row[(size_t)s * in_stride + q_width + rank + i]);
+        const float v = sum_parts(row + q_width + rank + i, in_stride, n_in);
         gate_out[(size_t)t * n_gate + i] = 1.f / (1.f + expf(-v));
     }
 }
@@ -64,7 +74,7 @@ int launch_prep(const void* in, int n_in, long long in_stride, int row_stride, i
                 const int* slot_of_token, const int* block_table, int max_pages, int T, cudaStream_t s) {
     const size_t smem = (size_t)(rank + 33) * sizeof(float);
     if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
-    RB_LAUNCH((latent_prep_kernel<IT, AT, WT>), dim3(T), dim3(128), smem, s, (const IT*)in, n_in, (size_t)in_stride, row_stride,
+    RB_LAUNCH((latent_prep_kernel<IT, AT, WT>), dim3(T), dim3(256), smem, s, (const IT*)in, n_in, (size_t)in_stride, row_stride,
               q_width, rank, n_gate, (const WT*)w, eps, (AT*)q_out, q_stride, gate_out, (AT*)cache, positions, slot_of_token,
               block_table, max_pages);
     RB_LAUNCH_CHECK();

@@ -18,13 +18,14 @@ namespace {
 constexpr int MAX_EPL = 16;   // experts per lane: up to 512 experts
 
 // ---- router logits: z[t, e] = sum_k x[t, k] * w[e, k], 32-bit FMA, w float32 ---------------------------------
-// A block takes TT tokens (their rows staged in shared memory as float32) and 8 experts, a warp one expert: its
-// lanes stream the expert's row with 16-byte loads, every lane multiplying its slice of k with the same slice of
-// the block's tokens, and the lanes' sums meet in a shuffle tree.  How k is dealt out depends on K only, so a
-// token's logits depend on nothing else in the batch.
+// A block takes TT tokens (their rows staged in shared memory as float32) and 8 * EW experts, a warp EW of them:
+// a lane takes its slice of k of the block's tokens from shared memory once and multiplies it with the same slice
+// of each of its experts' rows, which it streams with 16-byte loads; the lanes' sums meet in a shuffle tree.  How
+// k is dealt out depends on K only, so a token's logits depend on nothing else in the batch.  EW is 1 for a
+// handful of tokens (more blocks stream the router's rows) and 4 beyond (a quarter of the shared-memory reads).
 constexpr int RT_WARPS = 8;
 
-template <typename XT, int TT>
+template <typename XT, int TT, int EW>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 router_logits_kernel(const XT* __restrict__ x, long long ldx, const float* __restrict__ w, float* __restrict__ z, int ldz,
                      int T, int E, int K) {
@@ -32,61 +33,84 @@ router_logits_kernel(const XT* __restrict__ x, long long ldx, const float* __res
     pdl_wait();
     extern __shared__ __align__(16) float xs[];      // [TT][K]
     const int t0 = blockIdx.x * TT;
-    for (int idx = threadIdx.x; idx < TT * K; idx += blockDim.x) {
-        const int r = idx / K, k = idx - r * K;
-        xs[idx] = t0 + r < T ? to_f32(x[(size_t)(t0 + r) * ldx + k]) : 0.f;
+    if (sizeof(XT) == 2 && (K & 7) == 0 && (ldx & 7) == 0 && ((uintptr_t)x & 15) == 0) {
+        const int K8 = K >> 3;
+        for (int idx = threadIdx.x; idx < TT * K8; idx += blockDim.x) {
+            const int r = idx / K8, c = idx - r * K8;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (t0 + r < T) raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (size_t)(t0 + r) * ldx + c * 8);
+            const uint32_t ws[4] = {raw.x, raw.y, raw.z, raw.w};
+            float* d = xs + (size_t)r * K + c * 8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                d[2 * i] = __uint_as_float(ws[i] << 16);
+                d[2 * i + 1] = __uint_as_float(ws[i] & 0xFFFF0000u);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < TT * K; idx += blockDim.x) {
+            const int r = idx / K, k = idx - r * K;
+            xs[idx] = t0 + r < T ? to_f32(x[(size_t)(t0 + r) * ldx + k]) : 0.f;
+        }
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.y * RT_WARPS + warp;
-    if (e >= E) return;
-    const float* row = w + (size_t)e * K;
-    float acc[TT];
+    const int e0 = (blockIdx.y * RT_WARPS + warp) * EW;
+    if (e0 >= E) return;
+    float acc[EW][TT];
 #pragma unroll
-    for (int r = 0; r < TT; ++r) acc[r] = 0.f;
+    for (int j = 0; j < EW; ++j)
+#pragma unroll
+        for (int r = 0; r < TT; ++r) acc[j][r] = 0.f;
     if ((K & 3) == 0 && ((uintptr_t)w & 15) == 0) {
         const int K4 = K >> 2;
-        for (int k4 = lane; k4 < K4; k4 += 32 * 4) {           // four 16-byte loads in flight a lane
-            float4 wv[4];
+        for (int k4 = lane; k4 < K4; k4 += 32) {
+            float4 wv[EW];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                wv[u] = k4 + u * 32 < K4 ? reinterpret_cast<const float4*>(row)[k4 + u * 32] : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < EW; ++j)
+                wv[j] = e0 + j < E ? reinterpret_cast<const float4*>(w + (size_t)(e0 + j) * K)[k4] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (k4 + u * 32 >= K4) continue;
+            for (int r = 0; r < TT; ++r) {
+                const float4 xv = *reinterpret_cast<const float4*>(xs + (size_t)r * K + (size_t)k4 * 4);
 #pragma unroll
-                for (int r = 0; r < TT; ++r) {
-                    const float4 xv = *reinterpret_cast<const float4*>(xs + (size_t)r * K + (size_t)(k4 + u * 32) * 4);
-                    acc[r] = fmaf(wv[u].x, xv.x, acc[r]);
-                    acc[r] = fmaf(wv[u].y, xv.y, acc[r]);
-                    acc[r] = fmaf(wv[u].z, xv.z, acc[r]);
-                    acc[r] = fmaf(wv[u].w, xv.w, acc[r]);
+                for (int j = 0; j < EW; ++j) {
+                    acc[j][r] = fmaf(wv[j].x, xv.x, acc[j][r]);
+                    acc[j][r] = fmaf(wv[j].y, xv.y, acc[j][r]);
+                    acc[j][r] = fmaf(wv[j].z, xv.z, acc[j][r]);
+                    acc[j][r] = fmaf(wv[j].w, xv.w, acc[j][r]);
                 }
             }
         }
     } else {
         for (int k = lane; k < K; k += 32) {
-            const float wv = row[k];
 #pragma unroll
-            for (int r = 0; r < TT; ++r) acc[r] = fmaf(wv, xs[(size_t)r * K + k], acc[r]);
+            for (int j = 0; j < EW; ++j) {
+                const float wv = e0 + j < E ? w[(size_t)(e0 + j) * K + k] : 0.f;
+#pragma unroll
+                for (int r = 0; r < TT; ++r) acc[j][r] = fmaf(wv, xs[(size_t)r * K + k], acc[j][r]);
+            }
         }
     }
 #pragma unroll
-    for (int r = 0; r < TT; ++r) {
-        const float v = warp_sum(acc[r]);
-        if (lane == 0 && t0 + r < T) z[(size_t)(t0 + r) * ldz + e] = v;
-    }
+    for (int j = 0; j < EW; ++j)
+#pragma unroll
+        for (int r = 0; r < TT; ++r) {
+            const float v = warp_sum(acc[j][r]);
+            if (lane == 0 && t0 + r < T && e0 + j < E) z[(size_t)(t0 + r) * ldz + e0 + j] = v;
+        }
 }
 
 template <typename XT, int TT>
 int launch_router(const void* x, long long ldx, const float* w, float* z, int ldz, int T, int E, int K, cudaStream_t s) {
     const size_t smem = (size_t)TT * K * sizeof(float);
-    auto k = router_logits_kernel<XT, TT>;
+    const bool few = T <= 16;
+    auto k = few ? router_logits_kernel<XT, TT, 1> : router_logits_kernel<XT, TT, 4>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    dim3 grid((T + TT - 1) / TT, (E + RT_WARPS - 1) / RT_WARPS);
+    const int per_block = RT_WARPS * (few ? 1 : 4);
+    dim3 grid((T + TT - 1) / TT, (E + per_block - 1) / per_block);
     if (grid.y > 65535) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((k), grid, dim3(RT_WARPS * 32), smem, s, (const XT*)x, ldx, w, z, ldz, T, E, K);
     RB_LAUNCH_CHECK();

@@ -181,7 +181,9 @@ class Model:
             with scope(layer=i):
                 if getattr(block, "chains", False):
                     # a block may prepare the first norm of the block that follows it
-                    nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
+                    # (not across additions to the stream: they come before that norm)
+                    nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) and not sched[i + 1].add_input \
+                        and sched[i + 1].add_row is None else None
                     pending = block.forward(resid, pending, batch, cache.views[i], next_block=nxt)
                 else:
                     pending = block.forward(resid, pending, batch, cache.views[i])

@@ -157,7 +157,7 @@ def _lib():
         lib.rb_hold.argtypes = [_ll, _vp]
         lib.rb_embedding_pos.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp]
         lib.rb_residual_inject.argtypes = [_vp, _vp, _i, _ll, _vp, _vp, _i, _i, _i, _vp]
-        lib.rb_postnorm_add_norm.argtypes = [_vp, _vp, _i, _ll, _vp, _f, _vp, _f, _i, _vp, _i, _i, _i, _vp]
+        lib.rb_postnorm_add_norm.argtypes = [_vp, _vp, _i, _ll, _vp, _vp, _i, _vp, _f, _vp, _f, _i, _vp, _i, _i, _i, _vp]
         lib.rb_gated_act.argtypes = [_vp, _i, _i, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _f, _f, _i, _vp]
         lib.rb_router_logits.argtypes = [_vp, _i, _ll, _vp, _vp, _i, _i, _i, _i, _vp]
         lib.rb_gemm_tcgen05_grouped.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _i, _i, _f, _f, _vp, _vp]
@@ -169,7 +169,7 @@ def _lib():
         lib.rb_moe_gather.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]
         lib.rb_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _i, _vp]
         lib.rb_grouped_matmul.argtypes = [_vp, _i, _ll, _i, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _vp, _i,
-                                          _vp, _i, _vp]
+                                          _vp, _i, _i, _f, _f, _vp]
         lib.rb_gemm_tcgen05_set_wait.argtypes = [_ll, _i]
         lib.rb_gemm_tcgen05_set_wait.restype = None
         _sigs_done = True
@@ -882,27 +882,39 @@ def residual_inject(resid: torch.Tensor, delta: Optional[torch.Tensor] = None, o
     _check(rc, "residual_inject")
 
 
-@_profiled(lambda a, facts: _cost.add_norm(a["resid"].shape[0], a["resid"].shape[1], a["delta"].shape[0],
+@_profiled(lambda a, facts: _cost.add_norm(a["resid"].shape[0], a["resid"].shape[1],
+                                           a["top"] if a["row_of"] is not None else a["delta"].shape[0],
                                            _esz(a["out"]) if a["out"] is not None else 0, True, _esz(a["w_post"])))
 def postnorm_add_norm(resid: torch.Tensor, delta: torch.Tensor, w_post: torch.Tensor, eps_post: float,
-                      w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0, out: Optional[torch.Tensor] = None):
-    """resid [T, H] float32 += rmsnorm(sum of delta [S, T, H] float32) * w_post; with ``w_next`` and ``out`` [T, H]:
-    out = rmsnorm(resid) * w_next (the next sublayer's input)."""
+                      w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0, out: Optional[torch.Tensor] = None,
+                      row_of: Optional[torch.Tensor] = None, weights: Optional[torch.Tensor] = None, top: int = 0):
+    """resid [T, H] float32 += rmsnorm(d) * w_post; with ``w_next`` and ``out`` [T, H]: out = rmsnorm(resid) * w_next
+    (the next sublayer's input).  d is the sum of ``delta`` [S, T, H] float32, or, with ``row_of`` (int32 [T, top],
+    -1: none) and ``weights`` (float32 [T, top]), row t's weighted sum of the rows ``delta`` [R, H] it names."""
     T, H = resid.shape
     if resid.dtype != torch.float32 or not resid.is_contiguous():
         raise KernelError("postnorm_add_norm: resid must be contiguous float32")
-    if delta.dtype != torch.float32 or delta.dim() != 3 or delta.shape[1] < T or delta.shape[2] != H or \
-            delta.stride(2) != 1 or delta.stride(1) != H:
-        raise KernelError("postnorm_add_norm: delta must be float32 [S, >= T, H] with dense rows")
+    if row_of is not None:
+        if delta.dtype != torch.float32 or delta.dim() != 2 or delta.shape[1] != H or delta.stride(1) != 1 or \
+                weights is None or weights.dtype != torch.float32 or top < 1 or row_of.numel() < T * top or \
+                weights.numel() < T * top or not weights.is_contiguous():
+            raise KernelError("postnorm_add_norm: rows to sum must be float32 [R, H] with int32 places and float32 weights [T, top]")
+        n_delta, stride = 1, delta.stride(0)
+    else:
+        if delta.dtype != torch.float32 or delta.dim() != 3 or delta.shape[1] < T or delta.shape[2] != H or \
+                delta.stride(2) != 1 or delta.stride(1) != H:
+            raise KernelError("postnorm_add_norm: delta must be float32 [S, >= T, H] with dense rows")
+        n_delta, stride = delta.shape[0], delta.stride(0)
     if (w_next is None) != (out is None):
         raise KernelError("postnorm_add_norm: give both the next norm's weight and its output or neither")
     if w_post.numel() != H or (w_next is not None and (w_next.numel() != H or w_next.dtype != w_post.dtype)):
         raise KernelError("postnorm_add_norm: the norms' weights must be [H] of one type")
     if out is not None and (not out.is_contiguous() or out.shape[-1] != H or out.numel() < T * H):
         raise KernelError("postnorm_add_norm: out must be contiguous [T, H]")
-    rc = _lib().rb_postnorm_add_norm(_ptr(resid), _ptr(delta), delta.shape[0], delta.stride(0), _ptr(w_post),
-                                     float(eps_post), _ptr(w_next), float(eps_next), dtype_code(w_post.dtype), _ptr(out),
-                                     dtype_code(out.dtype) if out is not None else F32, T, H, _stream())
+    rc = _lib().rb_postnorm_add_norm(_ptr(resid), _ptr(delta), n_delta, stride,
+                                     None if row_of is None else _i32(row_of, "row_of"), _ptr(weights), int(top),
+                                     _ptr(w_post), float(eps_post), _ptr(w_next), float(eps_next), dtype_code(w_post.dtype),
+                                     _ptr(out), dtype_code(out.dtype) if out is not None else F32, T, H, _stream())
     _check(rc, "postnorm_add_norm")
 
 
@@ -1051,25 +1063,35 @@ def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m: int, row
         raise KernelError("head_matmul: row_scale must be contiguous float32 [T, G]")
     rc = _lib().rb_grouped_matmul(_ptr(x), dtype_code(x.dtype), x.stride(0), K, _ptr(w), dtype_code(w.dtype), N * K,
                                   _ptr(out), dtype_code(out.dtype), out.stride(0), N, m, N, K, G, None, 0,
-                                  _ptr(row_scale), G, _stream())
+                                  _ptr(row_scale), G, 0, 0.0, 1.0, _stream())
     _check(rc, "head_matmul")
 
 
 @_profiled(lambda a, facts: (a["w"].numel() * _esz(a["w"]) + a["x"].shape[0] * (a["w"].shape[2] * _esz(a["x"])
                                                                                + a["w"].shape[1] * _esz(a["out"])),
                              2 * a["x"].shape[0] * a["w"].shape[1] * a["w"].shape[2]))
-def tile_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, tile_rows: int):
+def tile_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, tile_rows: int,
+                act: Optional[str] = None, limit: float = 0.0, alpha: float = 1.0) -> bool:
     """Products by tiles of sorted rows: rows i * tile_rows .. of ``x`` [R, K] are multiplied with
-    w[tile_group[i]] ([G, N, K]) into the same rows of ``out`` [R, N]; a tile of group -1 is skipped."""
+    w[tile_group[i]] ([G, N, K]) into the same rows of ``out`` [R, N]; a tile of group -1 is skipped.
+    With ``act`` (bfloat16 on the tensor cores only; w's gate and up rows interleaved in blocks of 16) out is
+    [R, N / 2], the gated activation of the product (see ``gated_act``); False is returned, and nothing
+    launched, when the operands do not take that kernel."""
     G, N, K = w.shape
     R = x.shape[0]
-    if x.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != K or out.shape[1] != N or out.shape[0] != R or \
-            not w.is_contiguous() or R % tile_rows or tile_group.numel() < R // tile_rows:
+    if x.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != K or out.shape[1] != (N // 2 if act else N) or \
+            out.shape[0] != R or not w.is_contiguous() or R % tile_rows or tile_group.numel() < R // tile_rows:
         raise KernelError("tile_matmul: shapes or strides do not fit")
+    if act is not None and act not in GATED_ACTS:
+        raise KernelError(f"tile_matmul: unknown activation {act!r}")
     rc = _lib().rb_grouped_matmul(_ptr(x), dtype_code(x.dtype), x.stride(0), 0, _ptr(w), dtype_code(w.dtype), N * K,
                                   _ptr(out), dtype_code(out.dtype), out.stride(0), 0, R, N, K, G,
-                                  _i32(tile_group, "tile_group"), int(tile_rows), None, 0, _stream())
+                                  _i32(tile_group, "tile_group"), int(tile_rows), None, 0,
+                                  0 if act is None else GATED_ACTS[act] + 1, float(limit), float(alpha), _stream())
+    if act is not None and rc == 10001:
+        return False
     _check(rc, "tile_matmul")
+    return True
 
 
 @_profiled(lambda a, facts: ((a["w"].numel() * 2 + a["x"].shape[0] * (a["w"].shape[2] * 2 + a["out"].shape[1] * _esz(a["out"])),

@@ -72,6 +72,34 @@ class DeferredNorm:
         return self.norm.forward(self.resid, None, self.x.shape[0], write_back=False)
 
 
+@dataclass
+class RoutedRows:
+    """A routed feed-forward's result before the weighted sum over a token's choices: row t of the result is
+    sum_j weights[t, j] * rows[row_of[t, j]] (row_of -1: none).  Handed, instead of a delta, to an arrangement
+    that said it sums them itself (in the kernel that consumes the delta); ``materialize`` does it otherwise."""
+
+    rows: torch.Tensor        # [R, H] float32
+    row_of: torch.Tensor      # [T, top] int32
+    weights: torch.Tensor     # [T, top] float32
+    top: int
+    n_tokens: int
+
+    def materialize(self) -> torch.Tensor:
+        from .. import kernels
+        out = torch.empty((1, self.n_tokens, self.rows.shape[1]), dtype=torch.float32, device=self.rows.device)
+        kernels.moe_combine(self.rows, self.row_of, self.weights, self.n_tokens, self.top, out[0])
+        return out
+
+
+class NormedRows(DeferredNorm):
+    """What a block leaves for the block after it when it has already run that block's first norm: ``x`` are
+    the finished rows of ``norm`` (nothing is deferred; the residual holds every delta).  Only a block that
+    knows this type is handed one; any other norm treats it as 'nothing pending'."""
+
+    def materialize(self) -> torch.Tensor:
+        return self.x
+
+
 class Part:
     """Common face: tensors declared, tensors loaded."""
 

@@ -9,7 +9,8 @@ import torch
 from ..config.specs import LayerSpec
 from ..profile import scope
 from ..weights.decl import TensorDecl
-from .base import BuildEnv, ResidualSink, build_feed_forward, build_mixer, build_norm, register_arrangement
+from .base import (BuildEnv, NormedRows, ResidualSink, RoutedRows, build_feed_forward, build_mixer, build_norm,
+                   register_arrangement)
 
 
 # From this many tokens in a step a part is offered to add into the residual itself (the products of
@@ -114,8 +115,10 @@ class SandwichNormBlock:
     A sublayer's result (a delta, possibly as partial sums) is normalised on its own before it joins the
     residual stream, so it cannot ride along to the next norm as a pre-norm block's delta does.  One
     kernel adds the partial sums, normalises them, adds into the 32-bit residual and normalises that for
-    the sublayer that follows.  The block leaves nothing pending.  A layer without a feed-forward has
-    only the first half."""
+    the sublayer that follows: after the mixer the feed-forward's norm, after the feed-forward the first norm
+    of the block that follows when that is a block of this kind (it gets the rows as ``NormedRows``).  A routed
+    feed-forward's weighted sum over a token's experts happens in the same kernel.  Nothing is left pending.
+    A layer without a feed-forward has only the first half."""
 
     chains = True          # forward() accepts next_block
 
@@ -177,20 +180,39 @@ class SandwichNormBlock:
         out = None
         if nxt is not None:
             out = torch.empty((T, self.hidden), dtype=self.env.act_dtype, device=resid.device)
-        kernels.postnorm_add_norm(resid, delta, post.weight, post.eps, nxt.weight if nxt is not None else None,
-                                  nxt.eps if nxt is not None else 0.0, out)
+        w_next, eps_next = (nxt.weight, nxt.eps) if nxt is not None else (None, 0.0)
+        if isinstance(delta, RoutedRows):
+            kernels.postnorm_add_norm(resid, delta.rows, post.weight, post.eps, w_next, eps_next, out,
+                                      row_of=delta.row_of, weights=delta.weights, top=delta.top)
+        else:
+            kernels.postnorm_add_norm(resid, delta, post.weight, post.eps, w_next, eps_next, out)
         return out
 
     def forward(self, resid, pending, batch, view, next_block=None):
         T = batch.n_tokens
-        with scope(op="mixer_norm"):
-            xn = self.mixer_norm.forward(resid, pending, T)      # (adds whatever a different kind of layer before left pending)
+        if isinstance(pending, NormedRows) and pending.norm is self.mixer_norm:
+            xn = pending.x                                       # the block before has run this block's first norm
+        else:
+            with scope(op="mixer_norm"):
+                xn = self.mixer_norm.forward(resid, pending, T)  # (adds whatever a different kind of layer before left pending)
         delta = self.mixer.forward(xn, batch, view)
+        # the norm that follows the last sublayer: the next block's first, when that block takes the rows
+        after = next_block.mixer_norm if isinstance(next_block, SandwichNormBlock) and \
+            hasattr(next_block.mixer_norm, "weight") and next_block.mixer_norm.weight is not None and \
+            next_block.mixer_norm.weight.dtype == self.mixer_post.weight.dtype else None
         with scope(op="mixer_post_norm"):
-            xn = self._post(resid, delta, self.mixer_post, self.ff_norm, T)
+            xn = self._post(resid, delta, self.mixer_post, self.ff_norm if self.ff is not None else after, T)
         if self.ff is None:
-            return None
-        delta = self.ff.forward(xn, batch)
+            return self._handed(xn, after, resid)
+        if getattr(self.ff, "sums_later", False):
+            delta = self.ff.forward(xn, batch, sum_later=True)
+        else:
+            delta = self.ff.forward(xn, batch)
         with scope(op="ff_post_norm"):
-            self._post(resid, delta, self.ff_post, None, T)
-        return None
+            xn = self._post(resid, delta, self.ff_post, after, T)
+        return self._handed(xn, after, resid)
+
+    def _handed(self, rows, norm, resid):
+        if norm is None:
+            return None
+        return NormedRows(rows, None, norm.eps, self.hidden, norm, resid)

@@ -28,7 +28,7 @@ from ..config.specs import FeedForwardSpec, tensor_names
 from ..errors import ConfigError
 from ..profile import scope
 from ..weights.decl import TensorDecl
-from .base import BuildEnv, FeedForward, register_feed_forward
+from .base import BuildEnv, FeedForward, RoutedRows, register_feed_forward
 
 TENSOR_NAMES = {"router": "gate", "choice_bias": "e_score_correction_bias", "expert": "experts.{e}.", "gate": "gate_proj",
                 "up": "up_proj", "down": "down_proj"}
@@ -134,7 +134,9 @@ class RoutedMLP(FeedForward):
         nbytes = self.experts * self.hidden * 4 + used * 3 * self.inter * self.hidden * esz
         return nbytes, 2 * T * self.experts * self.hidden + 2 * T * self.top * 3 * self.inter * self.hidden
 
-    def forward(self, xn, batch):
+    sums_later = True      # forward() accepts sum_later=True and may then return RoutedRows (see parts.base)
+
+    def forward(self, xn, batch, sum_later=False):
         T = batch.n_tokens
         dev, act = self.env.device, self.env.act_dtype
         E, top = self.experts, self.top
@@ -161,6 +163,10 @@ class RoutedMLP(FeedForward):
         if tile == TENSOR_TILE:
             with scope(op="experts_gate_up"):
                 fused = kernels.tile_matmul_tc5(xs, self.gate_up, y, tile_group, self.act, self.limit, self.alpha)
+        if not fused and self.paired:
+            # the mma.sync product has the activation in its epilogue too, when the operands take it
+            with scope(op="experts_gate_up"):
+                fused = kernels.tile_matmul(xs, self.gate_up, y, tile_group, tile, self.act, self.limit, self.alpha)
         if not fused:
             gu = torch.empty((rows, 2 * self.inter), dtype=act, device=dev)
             with scope(op="experts_gate_up"):
@@ -171,7 +177,8 @@ class RoutedMLP(FeedForward):
         with scope(op="experts_down"):
             if not (tile == TENSOR_TILE and kernels.tile_matmul_tc5(y, self.down, out_rows, tile_group)):
                 kernels.tile_matmul(y, self.down, out_rows, tile_group, tile)
-        delta = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
+        routed = RoutedRows(out_rows, row_of, weights, top, T)
+        if sum_later:
+            return routed
         with scope(op="experts_sum"):
-            kernels.moe_combine(out_rows, row_of, weights, T, top, delta[0])
-        return delta
+            return routed.materialize()
