@@ -221,8 +221,13 @@ grouped_mma_kernel(const GP p) {
                 const int n = n0 + (wn * NT + j) * 8 + (lane & 3) * 2;
                 float v0 = acc[i][j][h * 2], v1 = acc[i][j][h * 2 + 1];
                 if (p.row_scale) { v0 *= sc; v1 *= sc; }
-                if (n < p.N) out[(size_t)m * p.ldo + n] = from_f32<OT>(v0);
-                if (n + 1 < p.N) out[(size_t)m * p.ldo + n + 1] = from_f32<OT>(v1);
+                OT* dst = out + (size_t)m * p.ldo + n;
+                if (sizeof(OT) == 2 && n + 1 < p.N && (((uintptr_t)dst) & 3) == 0) {
+                    *reinterpret_cast<uint32_t*>(dst) = mma_tiles::pack_bf16(v0, v1);      // both columns in one store
+                } else {
+                    if (n < p.N) dst[0] = from_f32<OT>(v0);
+                    if (n + 1 < p.N) dst[1] = from_f32<OT>(v1);
+                }
             }
         }
     }

@@ -532,7 +532,7 @@ def profile_table(model=None, layers=0, batch=BATCH, dtype="bfloat16", prompt=PR
     from . import StepEntry
     from .profile import Profiler, to_human
     cfg, n_full, eng = build_engine(layers, batch * (prompt + 64 * 2), batch, model=model, dtype=dtype)
-    ps = prompts(batch, prompt + steps, cfg.vocab_size, 3)
+    ps = prompts(batch, prompt + steps, eng.model.spec.vocab, 3)
 
     def run():
         slots = [eng.new_sequence() for _ in ps]
@@ -544,7 +544,7 @@ def profile_table(model=None, layers=0, batch=BATCH, dtype="bfloat16", prompt=PR
     run()
     with Profiler(eng.device, dtype=dtype) as prof:
         run()
-    print(f"{model or MODEL} layer sizes, {cfg.num_hidden_layers} of {n_full} layers, {dtype}, batch {batch}, "
+    print(f"{model or MODEL} layer sizes, {len(eng.model.spec.layers)} of {n_full} layers, {dtype}, batch {batch}, "
           f"prompts of {prompt} tokens, {steps} decode steps")
     print(to_human(prof.report(), layers=by_layer))
 

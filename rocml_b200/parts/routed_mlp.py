@@ -130,8 +130,10 @@ class RoutedMLP(FeedForward):
     def cost(self, q_lens, kv_lens):
         T = sum(q_lens)
         esz = 4 if self.env.mode == "float32" else 2
-        used = min(self.experts, T * self.top)
-        nbytes = self.experts * self.hidden * 4 + used * 3 * self.inter * self.hidden * esz
+        # which experts a step reads depends on its tokens; counted here: the experts T tokens touch when each
+        # picks ``top`` of them at random (all of them for a prompt, a part of them for a few tokens)
+        used = self.experts * (1.0 - (1.0 - self.top / self.experts) ** T)
+        nbytes = self.experts * self.hidden * 4 + int(used * 3 * self.inter * self.hidden * esz)
         return nbytes, 2 * T * self.experts * self.hidden + 2 * T * self.top * 3 * self.inter * self.hidden
 
     sums_later = True      # forward() accepts sum_later=True and may then return RoutedRows (see parts.base)

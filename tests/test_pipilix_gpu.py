@@ -513,3 +513,33 @@ def test_trace_replay_writes_what_the_step_returns(model, tmp_path):
     assert rel_err(got0, want0) < TOL["float32"]
     got3 = torch.from_numpy(np.fromfile(os.path.join(out, "3.f32"), dtype="<f4").reshape(-1, V))
     assert rel_err(got3, plain(a)[39:40]) < TOL["float32"]
+
+
+def test_the_command_line_generates_and_profiles(models):
+    """`python -m rocml_b200 generate` on a Pipilix folder: greedy tokens equal the plain implementation's (32-bit),
+    and --profile lists the design's own kernels."""
+    import os
+    import subprocess
+    import sys
+    name, cfg, by_dtype = models
+    f = by_dtype["float32"]
+    ids = prompt(12, 9, cfg["vocab"])
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "rocml_b200", "generate", "--model", f.folder, "--dtype", "float32",
+                        "--prompt-ids", ",".join(map(str, ids)), "-n", "5", "-t", "0", "--profile"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    toks = [int(x) for x in p.stdout.split("limits (")[0].split()]
+    seq = list(ids)
+    for t in toks:
+        logits = f(seq)[-1]
+        best = int(torch.argmax(logits))
+        if t != best:
+            top2 = torch.topk(logits, 2).values
+            assert float(top2[0] - logits[t]) < 1e-4 * float(top2[0].abs())
+        seq.append(t)
+    assert len(toks) == 5
+    for label in ("latent_norm_cache", "fold_queries", "unfold_values", "mixer_post_norm", "q+dkv"):
+        assert label in p.stdout, label
+    if any(L["mlp"] and L["mlp"]["kind"] == "moe" for L in cfg["layers"]):
+        assert "router" in p.stdout and "experts_gate_up" in p.stdout
