@@ -29,7 +29,7 @@ namespace {
 constexpr int ROWS = 16;       // query rows (token, head) per block
 constexpr int RW = 4;          // rows per warp
 constexpr int KT = 32;         // keys per tile: one per lane
-constexpr int MAX_DPL = 8;     // head dims per lane -> head size up to 256
+constexpr int MAX_DPL = 16;    // head dims per lane: head sizes up to 256 take 8 of them, up to 512 all 16
 constexpr float NEG_BIG = -1e30f;
 
 __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -40,8 +40,8 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
     return make_float4(a.x, a.y, b.x, b.y);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(128, 4)
+template <typename T, int DPL>
+__global__ void __launch_bounds__(128, DPL <= 8 ? 4 : 2)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int o_stride,
                          const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                          const int* __restrict__ block_table, int max_pages,
@@ -111,7 +111,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 
     int row_pos[RW], row_lo[RW];
     bool row_ok[RW];
-    float m[RW], l[RW], acc[RW][MAX_DPL];
+    float m[RW], l[RW], acc[RW][DPL];
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
         const int r = i * 4 + warp;               // the block's rows are dealt out over its four warps in turn
@@ -122,7 +122,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         m[i] = NEG_BIG;
         l[i] = 0.f;
 #pragma unroll
-        for (int j = 0; j < MAX_DPL; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < DPL; ++j) acc[i][j] = 0.f;
     }
 
     // A block with few rows (a decode step: one token, the group's heads) gives each warp one of them instead of
@@ -213,14 +213,14 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 l[i] = l[i] * alpha + warp_sum(p[i]);
                 m[i] = m_new;
 #pragma unroll
-                for (int dd = 0; dd < MAX_DPL; ++dd) acc[i][dd] *= alpha;
+                for (int dd = 0; dd < DPL; ++dd) acc[i][dd] *= alpha;
             }
             for (int jj = 0; jj < KT; ++jj) {
                 float pj[NR];
 #pragma unroll
                 for (int i = 0; i < NR; ++i) pj[i] = __shfl_sync(0xffffffffu, p[i], jj);
 #pragma unroll
-                for (int dd = 0; dd < MAX_DPL; ++dd) {
+                for (int dd = 0; dd < DPL; ++dd) {
                     const int d = lane + 32 * dd;
                     if (d < hd) {
                         const float vv = v_s[jj * hd + d];
@@ -246,14 +246,14 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
             const size_t pidx = ((size_t)t * nq + head) * n_chunks + c;
             if (lane == 0) { part_ml[pidx * 2] = m[i]; part_ml[pidx * 2 + 1] = l[i]; }
 #pragma unroll
-            for (int dd = 0; dd < MAX_DPL; ++dd) {
+            for (int dd = 0; dd < DPL; ++dd) {
                 const int d = lane + 32 * dd;
                 if (d < hd) part_acc[pidx * hd + d] = acc[i][dd];
             }
         } else {
             const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
 #pragma unroll
-            for (int dd = 0; dd < MAX_DPL; ++dd) {
+            for (int dd = 0; dd < DPL; ++dd) {
                 const int d = lane + 32 * dd;
                 if (d < hd) out[(size_t)t * o_stride + (size_t)head * hd + d] = from_f32<T>(acc[i][dd] * inv);
             }
@@ -323,7 +323,7 @@ int launch_attn(const void* q, int q_stride, void* out, int o_stride, const void
     const long long gx = (long long)((max_q_len + QB - 1) / QB) * n_chunks;
     if (gx > 0x7fffffffLL || (long long)nkv * head_chunks > 65535 || B > 65535) return RB_ERR_BAD_SIZE;
     const size_t smem = (size_t)(ROWS * hd + KT * (hd + 1) + KT * hd) * sizeof(float);
-    auto k = attention_generic_kernel<T>;
+    auto k = hd <= 256 ? attention_generic_kernel<T, 8> : attention_generic_kernel<T, MAX_DPL>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;

@@ -65,8 +65,13 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at once (each rounded up to 64); sizes the cache")
+                    help="most tokens live requests hold at once (padding not counted); sizes the cache")
     args = ap.parse_args(argv)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, device="cuda:0", max_tokens=args.max_tokens)
+    # The cache hands out pages of 64 tokens and a slot a request: every live request may hold one partly
+    # filled page beyond its tokens.  Room for that many more pages is added, for up to `slots` live requests.
+    n = max(1, args.max_tokens)
+    slots = min(n, max(64, 2 * ((n + 63) // 64)))
+    engine = Engine.from_folder(args.model, dtype=args.dtype, device="cuda:0", max_tokens=n + 63 * slots,
+                                max_slots=slots)
     replay(engine, sys.stdin, args.out)
     return 0

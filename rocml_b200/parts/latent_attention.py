@@ -52,9 +52,9 @@ class LatentAttention(Mixer):
         self.rank = int(p["kv_rank"])
         if min(self.heads, self.hd, self.vd, self.rank) <= 0:
             raise ConfigError("latent attention: heads, head sizes and the latent's size must be positive")
-        if self.rank > 256:
+        if self.rank > 512:
             raise ConfigError(f"latent attention: a latent of {self.rank} numbers is not supported (the attention "
-                              "kernels take up to 256)")
+                              "kernels take up to 512)")
         if spec.position.kind != "none":
             raise ConfigError("latent attention: a rotated part of queries and keys is not built")
         self.eps = float(p.get("latent_norm_eps", 1e-6))

@@ -466,6 +466,27 @@ def test_a_far_key_that_must_and_must_not_be_seen(tmp_path, dtype):
         assert rel_err(torch.cat(got), want[places]) < TOL[dtype], cut
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_latent_wider_than_the_tensor_core_kernels_take(tmp_path, dtype):
+    """A latent of 320 numbers (the plain attention kernel's wide variant), a prompt across a page border and a
+    window's edge, then six tokens one by one."""
+    from rocml_b200 import StepEntry
+    cfg = {"architecture": "Pipilix", "vocab": 80, "width": 96, "embedding": {"scale": 4.0}, "norm": {"eps": 1e-6},
+           "logit_scale": 1.0,
+           "layers": [{"type": "latent_attention",
+                       "mixer": {"heads": 2, "dim": 24, "vdim": 16, "kv_rank": 320, "scale": 0.2, "mask": {"size": 40}},
+                       "mlp": {"kind": "dense", "ff": 64}}]}
+    folder = write_pipilix(str(tmp_path / "wide"), cfg, seed=12, std=0.06, sharp=2.0)
+    f = Folder(folder)
+    ids = prompt(21, 106, 80)
+    eng = engine(folder, dtype)
+    slot = eng.new_sequence()
+    got = [eng.step([StepEntry(slot, ids[:100], list(range(100)))]).clone()]
+    got += [eng.step([StepEntry(slot, [ids[t]], [0])]).clone() for t in range(100, 106)]
+    eng.release(slot)
+    assert_rows(torch.cat(got), f(ids), f.calls(ids), dtype, f"latent 320 {dtype}")
+
+
 def test_greedy_generation_through_the_entry_point(model):
     """Engine.generate (the loop, the scheduler of batches, the GPU sampler) in 32-bit gives the plain
     implementation's greedy tokens; more requests than a batch holds, so slots are used again."""

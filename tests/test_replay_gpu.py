@@ -109,12 +109,19 @@ def test_trace_run_in_every_way_of_cutting(name, dtype, tmp_path):
 
 
 def test_trace_run_refuses_more_than_the_cache_holds(tmp_path):
+    """--max-tokens 64 sizes the cache for 64 tokens and a partly filled page for each of up to 64 requests: 64 pages.
+    Two requests of 60 tokens fit (a page each); 45 requests of 100 tokens (two pages each) do not."""
     cfg = CONFIGS["A"]
     folder = write_model(str(tmp_path / "model"), cfg, seed=1)
-    line = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": prompt(1, 60, 256), "want": [59]},
-                                              {"id": "b", "tokens": prompt(2, 60, 256), "want": [59]}], "end": []})
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype",
-                           "float32", "--out", str(tmp_path / "o"), "--max-tokens", "64"],
-                          input=line + "\n", capture_output=True, text=True, timeout=300)
-    assert proc.returncode != 0 and "CacheFull" in proc.stderr      # two requests of 60 need two pages of 64
+
+    def run(n_requests, length):
+        line = json.dumps({"step": 0, "entries": [{"id": f"r{i}", "tokens": prompt(i, length, 256), "want": [length - 1]}
+                                                  for i in range(n_requests)], "end": []})
+        return subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype",
+                               "float32", "--out", str(tmp_path / f"o{n_requests}"), "--max-tokens", "64"],
+                              input=line + "\n", capture_output=True, text=True, timeout=300)
+    ok = run(2, 60)
+    assert ok.returncode == 0 and "done 0" in ok.stdout, ok.stderr[-2000:]
+    proc = run(45, 100)
+    assert proc.returncode != 0 and "CacheFull" in proc.stderr
     assert "done 0" not in proc.stdout
