@@ -1067,16 +1067,26 @@ def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m: int, row
     _check(rc, "head_matmul")
 
 
-@_profiled(lambda a, facts: (a["w"].numel() * _esz(a["w"]) + a["x"].shape[0] * (a["w"].shape[2] * _esz(a["x"])
-                                                                               + a["w"].shape[1] * _esz(a["out"])),
-                             2 * a["x"].shape[0] * a["w"].shape[1] * a["w"].shape[2]))
+def _tile_cost(a, facts):
+    """The weights of the groups a step touches (``used``; all of them if not said), the rows in and out; the rows'
+    operations (``rows_used`` of them, the buffer's otherwise)."""
+    G, N, K = a["w"].shape
+    used = G if a.get("used") is None else min(G, a["used"])
+    rows = a["x"].shape[0] if a.get("rows_used") is None else a["rows_used"]
+    return (int(used * N * K * _esz(a["w"])) + rows * (K * _esz(a["x"]) + a["out"].shape[1] * _esz(a["out"])),
+            2 * rows * N * K)
+
+
+@_profiled(_tile_cost)
 def tile_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, tile_rows: int,
-                act: Optional[str] = None, limit: float = 0.0, alpha: float = 1.0) -> bool:
+                act: Optional[str] = None, limit: float = 0.0, alpha: float = 1.0, used: Optional[float] = None,
+                rows_used: Optional[int] = None) -> bool:
     """Products by tiles of sorted rows: rows i * tile_rows .. of ``x`` [R, K] are multiplied with
     w[tile_group[i]] ([G, N, K]) into the same rows of ``out`` [R, N]; a tile of group -1 is skipped.
     With ``act`` (bfloat16 on the tensor cores only; w's gate and up rows interleaved in blocks of 16) out is
     [R, N / 2], the gated activation of the product (see ``gated_act``); False is returned, and nothing
-    launched, when the operands do not take that kernel."""
+    launched, when the operands do not take that kernel.  ``used`` (groups that have rows) and ``rows_used`` (rows
+    that hold a token) only tell a profiler what the launch had to read and compute."""
     G, N, K = w.shape
     R = x.shape[0]
     if x.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != K or out.shape[1] != (N // 2 if act else N) or \
@@ -1094,10 +1104,10 @@ def tile_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group:
     return True
 
 
-@_profiled(lambda a, facts: ((a["w"].numel() * 2 + a["x"].shape[0] * (a["w"].shape[2] * 2 + a["out"].shape[1] * _esz(a["out"])),
-                              2 * a["x"].shape[0] * a["w"].shape[1] * a["w"].shape[2])))
+@_profiled(_tile_cost)
 def tile_matmul_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, act: Optional[str] = None,
-                    limit: float = 0.0, alpha: float = 1.0) -> bool:
+                    limit: float = 0.0, alpha: float = 1.0, used: Optional[float] = None,
+                    rows_used: Optional[int] = None) -> bool:
     """``tile_matmul`` for tiles of 128 rows on the tcgen05 tensor cores (the persistent product, each row tile
     taking its group's weight): x bfloat16 [R, K], w bfloat16 [G, N, K], out bfloat16 or float32 [R, N].  With
     ``act`` every group's rows of w alternate in blocks of 16 between gate and up, and out is bfloat16 [R, N / 2]

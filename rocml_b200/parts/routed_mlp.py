@@ -106,6 +106,10 @@ class RoutedMLP(FeedForward):
         esz = 4 if self.env.mode == "float32" else 2
         return self.experts * self.hidden * 4 + self.experts * 3 * self.inter * self.hidden * esz
 
+    def _expected_experts(self, n_tokens: int) -> float:
+        """The experts ``n_tokens`` tokens touch when each picks ``top`` of them at random."""
+        return self.experts * (1.0 - (1.0 - self.top / self.experts) ** n_tokens)
+
     def _tensor_tiles(self, n_tokens: int) -> bool:
         """Whether this step's products take the tcgen05 kernel: bfloat16, enough rows, sizes it addresses."""
         return (self.paired and self.env.act_dtype == torch.bfloat16 and n_tokens * self.top >= TENSOR_TILE_MIN_ROWS
@@ -132,7 +136,7 @@ class RoutedMLP(FeedForward):
         esz = 4 if self.env.mode == "float32" else 2
         # which experts a step reads depends on its tokens; counted here: the experts T tokens touch when each
         # picks ``top`` of them at random (all of them for a prompt, a part of them for a few tokens)
-        used = self.experts * (1.0 - (1.0 - self.top / self.experts) ** T)
+        used = self._expected_experts(T)
         nbytes = self.experts * self.hidden * 4 + int(used * 3 * self.inter * self.hidden * esz)
         return nbytes, 2 * T * self.experts * self.hidden + 2 * T * self.top * 3 * self.inter * self.hidden
 
@@ -162,23 +166,24 @@ class RoutedMLP(FeedForward):
             kernels.moe_gather(xn, ids, place, starts, T, top, xs, row_of)
         y = torch.empty((rows, self.inter), dtype=act, device=dev)
         fused = False
+        told = {"used": self._expected_experts(T), "rows_used": T * top}     # for a profiler's accounts only
         if tile == TENSOR_TILE:
             with scope(op="experts_gate_up"):
-                fused = kernels.tile_matmul_tc5(xs, self.gate_up, y, tile_group, self.act, self.limit, self.alpha)
+                fused = kernels.tile_matmul_tc5(xs, self.gate_up, y, tile_group, self.act, self.limit, self.alpha, **told)
         if not fused and self.paired:
             # the mma.sync product has the activation in its epilogue too, when the operands take it
             with scope(op="experts_gate_up"):
-                fused = kernels.tile_matmul(xs, self.gate_up, y, tile_group, tile, self.act, self.limit, self.alpha)
+                fused = kernels.tile_matmul(xs, self.gate_up, y, tile_group, tile, self.act, self.limit, self.alpha, **told)
         if not fused:
             gu = torch.empty((rows, 2 * self.inter), dtype=act, device=dev)
             with scope(op="experts_gate_up"):
-                kernels.tile_matmul(xs, self.gate_up, gu, tile_group, tile)
+                kernels.tile_matmul(xs, self.gate_up, gu, tile_group, tile, **told)
             with scope(op="experts_act"):
                 kernels.gated_act(gu, y, self.act, self.limit, self.alpha, paired=self.paired)
         out_rows = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         with scope(op="experts_down"):
-            if not (tile == TENSOR_TILE and kernels.tile_matmul_tc5(y, self.down, out_rows, tile_group)):
-                kernels.tile_matmul(y, self.down, out_rows, tile_group, tile)
+            if not (tile == TENSOR_TILE and kernels.tile_matmul_tc5(y, self.down, out_rows, tile_group, **told)):
+                kernels.tile_matmul(y, self.down, out_rows, tile_group, tile, **told)
         routed = RoutedRows(out_rows, row_of, weights, top, T)
         if sum_later:
             return routed

@@ -116,12 +116,13 @@ PIPILIX_C = {
                _layer(_latent(1, 40, 12, 28, 33, 0.15), _moe(20, 1.0, 7, 2))],
 }
 # PD: a width that is a multiple of four only, more heads than one block of the decode kernel takes (20 and 17 on
-# latents of 64 and 128), a single expert, and a window that ends inside the second page
+# latents of 64 and 128), a single expert, a window that ends inside the second page, and a layer whose sizes are all odd
 PIPILIX_D = {
     "architecture": "Pipilix", "vocab": 150, "width": 100, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
     "logit_scale": 1.5, "loop": {"start": 0, "stop": 1, "times": 2},
     "layers": [_layer(_latent(20, 8, 8, 64, 50, 0.4), _moe(32, 0.9, 1, 1)),
-               _layer(_latent(17, 16, 8, 128, 90, 0.3), _dense(64))],
+               _layer(_latent(17, 16, 8, 128, 90, 0.3), _dense(64)),
+               _layer(_latent(3, 7, 5, 37, 31, 0.45), _moe(9, 1.2, 3, 2))],
 }
 PIPILIX = {"PA": PIPILIX_A, "PB": PIPILIX_B, "PC": PIPILIX_C, "PD": PIPILIX_D}
 
