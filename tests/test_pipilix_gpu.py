@@ -113,7 +113,7 @@ def test_additions_between_layers():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("G, N, K, T", [(3, 20, 12, 7), (4, 32, 16, 16), (6, 96, 64, 70), (2, 40, 24, 200), (5, 8, 36, 33)])
+@pytest.mark.parametrize("G, N, K, T", [(3, 20, 12, 7), (4, 32, 16, 16), (7, 88, 48, 70), (2, 40, 24, 200), (5, 8, 36, 33)])
 def test_products_head_by_head(dtype, G, N, K, T):
     """Both row tiles, the tensor-core and the FMA kernel (sizes off 8 take the latter), strided rows, a gate a row."""
     from rocml_b200 import kernels
