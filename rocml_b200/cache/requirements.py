@@ -11,12 +11,32 @@ import torch
 class KVRequirement:
     """Keys and values of every position (window None) or of the last ``window`` positions.
     ``shared_values``: one tensor serves as both (a layer that caches a single vector a token, from
-    which it derives keys and values); ``view.v`` is then ``view.k``."""
+    which it derives keys and values); ``view.v`` is then ``view.k``.  ``chunk``: a query reads only
+    the keys of its own block of that many positions (blocks counted from position 0), so the pages
+    of earlier blocks come back as the sequence grows."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     shared_values: bool = False
+    chunk: Optional[int] = None
+
+    def first_needed(self, length: int) -> int:
+        """The lowest position that a query at position >= ``length`` can still read (0: everything stays)."""
+        if self.window is not None:
+            return max(0, length - self.window + 1)
+        if self.chunk is not None:
+            return length - length % self.chunk
+        return 0
+
+    @property
+    def releases(self) -> bool:
+        return self.window is not None or self.chunk is not None
+
+    @property
+    def span(self) -> Optional[int]:
+        """The most positions behind a query that it can read, when that is bounded."""
+        return self.window if self.window is not None else self.chunk
 
 
 @dataclass(frozen=True)

@@ -101,24 +101,25 @@ class KVGroup:
                     raise CacheFull(
                         f"the cache has {free} free pages of {PAGE} tokens when piece {n_piece} of the step "
                         f"starts, {todo} are needed (group of {self.n_entries} layers, {self.n_pages} pages in all"
-                        + (f", window of {self.window} tokens" if self.window else "") + ")")
+                        + (f", window of {self.req.span} tokens" if self.req.releases else "") + ")")
                 free -= todo
                 st[1] = max(st[1], need)
-            if self.window is None:
+            if not self.req.releases:
                 continue
             for slot, _ in piece:
                 st = state[slot]
-                keep_from = max(0, st[2] - self.window + 1) // PAGE
+                keep_from = self.req.first_needed(st[2]) // PAGE
                 if keep_from > st[0]:
                     free += max(0, min(keep_from, st[1]) - st[0])
                     st[0] = keep_from
 
     def release_out_of_window(self, slot: int, length: int) -> None:
         """After a step that left the sequence ``length`` long: the next query sits at a
-        position >= length and reads keys >= length - window + 1; pages wholly below go back."""
-        if self.window is None:
+        position >= length and reads keys >= length - window + 1 (or from the start of its block of
+        positions); pages wholly below go back."""
+        if not self.req.releases:
             return
-        keep_from = max(0, length - self.window + 1) // PAGE
+        keep_from = self.req.first_needed(length) // PAGE
         row = self.table_host[slot]
         start = self._released_upto.get(slot, 0)
         for p in range(start, keep_from):
@@ -254,8 +255,8 @@ class SequenceCache:
         own: Dict[int, CacheView] = {}
         for req, members in kv_members.items():
             n_pages = self.n_pages
-            if req.window is not None and max_step_tokens:
-                per_seq = pages_for(req.window + max_step_tokens) + 1
+            if req.releases and max_step_tokens:
+                per_seq = pages_for(req.span + max_step_tokens) + 1
                 n_pages = min(n_pages, max_slots * per_seq)
             g = KVGroup(req, len(members), n_pages, max_slots, self.max_pages_per_seq, dtype, device)
             self.kv_groups.append(g)

@@ -44,7 +44,9 @@ class PositionSpec:
     """Position encoding applied to queries and keys inside a mixer.
 
     kind "rope_neox": rotate-half rotary embedding over the first ``rot_dim``
-    dimensions of every head with base ``theta``; kind "none": nothing.
+    dimensions of every head with base ``theta``; kind "rope_pairs": the same with
+    neighbouring entries (2i, 2i + 1) as pairs; both take the parameter ``scaling``
+    ({factor, low, high, original}: long wavelengths stretched); kind "none": nothing.
     As a model's ``input_position`` (added to the embedding output, not applied inside a mixer):
     kind "sinusoid": entry 2i of the vector is sin(pos * theta^(-2i / width)), entry 2i + 1 the cosine.
     """
@@ -68,14 +70,21 @@ class MixerSpec:
     qk_norm_eps, window (None: every earlier key; n: the last n keys, the
     query's own position included), scale (None: 1/sqrt(head_dim)),
     names (the tensor-name stems under the layer's mixer prefix, by role:
-    q, k, v, o, q_norm, k_norm; default q_proj, k_proj, v_proj, o_proj,
-    q_norm, k_norm).
+    q, k, v, o, q_norm, k_norm, gate; default q_proj, k_proj, v_proj, o_proj,
+    q_norm, k_norm, gate_proj), v_head_dim (the value heads' size when it is not
+    head_dim), chunk (a query sees the earlier keys of its own block of that many
+    positions, blocks counted from position 0; not together with window), gated (head
+    n's result is multiplied by sigmoid(Wgate x)_n before the output projection).
     """
 
     kind: str
     params_items: Tuple[Tuple[str, Any], ...] = ()
     position: PositionSpec = PositionSpec(kind="none")
 
+    # Kind "linear_attention" (a decayed running sum S = d_h S + k v^T per head instead of a softmax; state of fixed
+    # size a sequence): n_heads, head_dim, v_head_dim, decay (one number a head), qk_activation and v_activation
+    # ("none" | "silu"), k_scale, out_norm ("per_head" | "all_heads") with out_norm_eps and out_norm_weight (bool),
+    # gate_activation ("silu" | "sigmoid"), names (roles q, k, v, gate, o, out_norm).
     # Kind "latent_attention" (keys and values unfolded from one cached latent vector a token): n_heads, head_dim
     # (queries and keys), v_head_dim, kv_rank, latent_norm_eps, window, scale, gated (a sigmoid gate per head on the
     # attention's output, read from the mixer's input), names (roles q, down, latent_norm, up_k, up_v, gate, o).

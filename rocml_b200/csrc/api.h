@@ -32,12 +32,17 @@ int rb_postnorm_add_norm(float* resid, const float* delta, int n_delta, long lon
                          const float* weights, int top, const void* w_post, float eps_post, const void* w_next,
                          float eps_next, int w_dtype, void* out, int out_dtype, int n_rows, int H, void* stream);
 
-// [gate | up] halves -> out; kind 0: silu(g) * u; kind 1: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u) + 1).
+// [gate | up] halves -> out; kind 0: silu(g) * u; kind 1: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u) + 1);
+// kind 2: gelu(g) * u, gelu in its tanh form.
 // paired: gates and ups alternate in blocks of 16 columns instead of lying in two halves.
 int rb_gated_act(const void* in, int in_dtype, int n_in, long long in_stride, long long in_ld, void* out, int out_dtype,
                  long long out_ld, int rows, int I, int kind, float limit, float alpha, int paired, void* stream);
 
 int rb_scale(float* x, long long n, float factor, void* stream);
+
+// out[t, h, :out_w] = in[t, h, :out_w] * gate[t, h] for heads of in_w (>= out_w) values; gate float32 or absent.
+int rb_head_gate(const void* in, long long ld_in, int in_w, void* out, long long ld_out, int out_w, const float* gate,
+                 int heads, int T, int dtype, void* stream);
 
 // A latent-attention layer's projection rows [queries | latent | gate logits]: latent normalised into the paged
 // cache, queries (when q_out is given) and sigmoid(gates) written out (latent.cu).
@@ -49,13 +54,32 @@ int rb_latent_prep(const void* in, int in_dtype, int n_in, long long in_stride, 
 // Routed experts (routing.cu).  Router logits z[T, E] = x[T, K] . w[E, K]^T with 32-bit FMA, w float32.
 int rb_router_logits(const void* x, int x_dtype, long long ldx, const float* w, float* z, int ldz, int T, int E, int K,
                      void* stream);
+// n_groups > 1: only experts of the keep_groups best groups of neighbours can be chosen (a group's score: its two
+// largest scores added); renormalize: weights divided by their sum + norm_eps.
 int rb_moe_route(const float* z, int ldz, const void* bias, int bias_dtype, const int* slot_of_token, int T, int E,
-                 int top, int* ids, float* weights, int* place, int* counts, void* stream);
+                 int top, int* ids, float* weights, int* place, int* counts, int n_groups, int keep_groups,
+                 int renormalize, float norm_eps, void* stream);
 int rb_moe_plan(const int* counts, int E, int tile_rows, int max_tiles, int* starts, int* tile_group, void* stream);
 int rb_moe_gather(const void* x, int dtype, int H, const int* ids, const int* place, const int* starts, int T, int top,
                   void* rows, int* row_of, void* stream);
+// extra (optional): [n_extra][T, H] partial sums added to every token's row, times sigmoid(extra_gate[t * ld]) when
+// extra_gate is given.
 int rb_moe_combine(const float* y, long long ldy, const int* row_of, const float* weights, int T, int top, float* out,
-                   int H, void* stream);
+                   int H, const float* extra, int n_extra, long long extra_stride, const float* extra_gate,
+                   int extra_gate_ld, void* stream);
+
+// Linear attention with a fixed decay per head (linear_attention.cu).  The step's tokens go through
+// S = decay[h] * S + k v^T, o = S^T q per (sequence, head), the state [slots, heads, dim, vdim] float32 read and
+// written in place; q, k, v are columns q_off, k_off, v_off of the projection rows (n_in partial sums added first);
+// act 1: silu on q and k (act_qk) or v (act_v); k is multiplied by k_scale.  out float32 [T, heads * vdim].
+int rb_decay_scan(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_off, int k_off,
+                  int v_off, int heads, int dim, int vdim, int act_qk, int act_v, float k_scale, const float* decay,
+                  float* state, const int* seq_slot, const int* cu_q, int B, float* out, int ld_out, void* stream);
+// out = o / rms(o over each of `groups` column groups) (* w) * act(gate), gate = columns g_off.. of the projection
+// rows; gate_act 0: none, 1: silu, 2: sigmoid.
+int rb_group_norm_gate(const float* o, int ld_o, const void* proj, int proj_dtype, int n_in, long long in_stride,
+                       int row_stride, int g_off, const void* w, int w_dtype, float eps, int groups, int W, int gate_act,
+                       void* out, int out_dtype, int ld_out, const int* slot_of_token, int T, void* stream);
 
 // Many small products in one launch, by head or by tiles of sorted rows (grouped_matmul.cu).
 int rb_grouped_matmul(const void* x, int x_dtype, long long ldx, int x_col_stride, const void* w, int w_dtype,
@@ -71,7 +95,8 @@ int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, long long in_s
                           int act_dtype, int q_stride, int T, int nq, int nkv, int hd, const void* q_norm_w,
                           const void* k_norm_w, int w_dtype, float eps, const float* inv_freq, int rot_dim,
                           const int* positions, const int* slot_of_token, const int* block_table, int max_pages,
-                          void* k_cache, void* v_cache, int write_kv, const void* cos_sin, void* stream);
+                          void* k_cache, void* v_cache, int write_kv, const void* cos_sin, int vd, int hdp,
+                          int interleaved, int n_gate, float* gate_out, void* stream);
 
 int rb_rope_table(const int* positions, const float* inv_freq, int T, int half, void* out, void* stream);
 

@@ -206,7 +206,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int i = threadIdx.x; i < n_seqs; i += WARPS * 32) {
             const int ps = kv_len[i] - 1;
             int P = 0;
-            if (seq_slot[i] >= 0 && ps >= 0) P = ps / CHUNK - (window > 0 ? max(0, ps - window + 1) / CHUNK : 0) + 1;
+            if (seq_slot[i] >= 0 && ps >= 0) P = ps / CHUNK - span_lo(ps, window) / CHUNK + 1;
             s_pages[i] = P;
         }
         __syncthreads();
@@ -229,7 +229,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if (slot < 0) return;
     const int t = cu_q[b];
     const int pos = kv_len[b] - 1;
-    const int win_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int win_lo = span_lo(pos, window);
     // this block's pages: [c * ppb, (c + 1) * ppb), cut at the sequence's end; PROP: what the run holds
     // of the sequence's visited pages
     if (PROP) {

@@ -4,7 +4,7 @@
 // decoded tokens: every query row (token, head) attends to the keys of its own sequence at
 // positions lo..pos with pos the token's absolute position (causal, inclusive:
 // rocml-kernels/kernels/attn_prefill.hip:57-60,121) and lo = max(0, pos - window + 1) when the
-// layer has a window.  Query head h reads key/value head h / g (attn_decode.hip:108); the
+// layer has a window (a negative `window` means blocks of that many positions: rb::span_lo).  Query head h reads key/value head h / g (attn_decode.hip:108); the
 // score is (q . k) * scale, scale applied after the dot (attn_decode.hip:158); softmax is an
 // online max/sum in 32-bit with expf (attn_decode.hip:160-170); o = sum p v / l
 // (attn_prefill.hip:201-203).
@@ -118,7 +118,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         const int qi = tok0 + r / HG, hg = hc * HG + r % HG;
         row_ok[i] = r < QB * HG && qi < q_len && hg < g;
         row_pos[i] = pos0 + qi;
-        row_lo[i] = window > 0 ? max(0, row_pos[i] - window + 1) : 0;
+        row_lo[i] = span_lo(row_pos[i], window);
         m[i] = NEG_BIG;
         l[i] = 0.f;
 #pragma unroll
@@ -141,7 +141,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     // key range of the whole block, then of this chunk
     const int last_tok = min(tok0 + QB, q_len) - 1;
     int hi = pos0 + last_tok;                                       // inclusive
-    int lo = window > 0 ? max(0, pos0 + tok0 - window + 1) : 0;
+    int lo = span_lo(pos0 + tok0, window);
     if (chunk > 0) {
         lo = max(lo, c * chunk);
         hi = min(hi, (c + 1) * chunk - 1);
@@ -280,7 +280,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     if (slot_of_token[t] < 0) return;
     const int pos = positions[t];
     const int c_hi = min(n_chunks - 1, pos / chunk);
-    const int c_lo = window > 0 ? max(0, pos - window + 1) / chunk : 0;
+    const int c_lo = span_lo(pos, window) / chunk;
     const size_t base = ((size_t)t * nq + head) * n_chunks;
     float* w = w_s + (size_t)warp * n_chunks;
     float M = NEG_BIG;

@@ -53,7 +53,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int kvh = head / (nq / nkv);
     const int rows_here = min(BM, q_len - m0);
     const int hi = pos0 + m0 + rows_here - 1;           // last key any row of the block may see
-    const int lo = window > 0 ? max(0, pos0 + m0 - window + 1) : 0;
+    const int lo = span_lo(pos0 + m0, window);
     const int kt_first = lo / BN, kt_last = hi / BN;
     const int* table = block_table + (size_t)slot * max_pages;
 
@@ -121,7 +121,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             for (int e = 0; e < 4; ++e) {
                 const int key = kt * BN + j * 8 + t * 2 + (e & 1);
                 const int r = e >> 1;
-                const bool ok = key <= row_pos[r] && (window <= 0 || key > row_pos[r] - window);
+                const bool ok = key <= row_pos[r] && key >= span_lo(row_pos[r], window);
                 s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
                 mx[r] = fmaxf(mx[r], s[j][e]);
             }

@@ -147,7 +147,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int kvh = head / (nq / nkv);
     const int rows_here = min(BMQ, q_len - m0);
     const int hi = pos0 + m0 + rows_here - 1;
-    const int lo = window > 0 ? max(0, pos0 + m0 - window + 1) : 0;
+    const int lo = rb::span_lo(pos0 + m0, window);
     const int kt_first = lo / BNK, kt_last = hi / BNK;
     const int n_tiles = kt_last - kt_first + 1;
     const int* table = block_table + (size_t)slot * max_pages;
@@ -285,11 +285,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // special-function instruction for 2^x.
             // a tile that every row of this warp sees whole needs no mask
             const int warp_first_pos = pos0 + m0 + quarter * 32;
-            if (!(key0 + BNK - 1 <= warp_first_pos && (window <= 0 || key0 > warp_first_pos + 31 - window))) {
+            if (!(key0 + BNK - 1 <= warp_first_pos && key0 >= rb::span_lo(warp_first_pos + 31, window))) {
 #pragma unroll
                 for (int i = 0; i < BNK; ++i) {
                     const int key = key0 + i;
-                    const bool ok = key <= row_pos && (window <= 0 || key > row_pos - window);
+                    const bool ok = key <= row_pos && key >= rb::span_lo(row_pos, window);
                     sv[i] = ok ? sv[i] : -INFINITY;
                 }
             }

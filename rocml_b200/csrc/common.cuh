@@ -82,6 +82,13 @@ inline cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The lowest key position a query at `pos` sees under a layer's mask, carried in one integer `window`:
+// 0: every earlier key; n > 0: the last n keys (its own included); -n: the keys of its own block of n
+// positions, blocks counted from position 0 of the sequence.  Never decreases as pos grows.
+__device__ __forceinline__ int span_lo(int pos, int window) {
+    return window > 0 ? max(0, pos - window + 1) : (window < 0 ? pos - pos % (-window) : 0);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 
@@ -90,6 +97,12 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
     return __float2bfloat16_rn(v);
 }
+
+// gelu in its tanh form: z / 2 * (1 + tanh(sqrt(2 / pi) * (z + 0.044715 z^3))), 32-bit
+__device__ __forceinline__ float gelu_tanh(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -553,6 +553,7 @@ extern "C" int rb_postnorm_add_norm(float* resid, const float* delta, int n_delt
 // (i / 16) * 32 + i % 16, its up 16 columns on); out: [rows, I].
 //   kind 0: silu(g) * u, silu(g) = g / (1 + exp(-g))
 //   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(alpha * g') * (u' + 1)
+//   kind 2: gelu(g) * u in its tanh form, gelu(g) = g / 2 * (1 + tanh(sqrt(2 / pi) * (g + 0.044715 g^3)))
 template <typename IT, typename OT>
 __global__ void gated_act_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, size_t in_ld, OT* __restrict__ out,
                                  size_t out_ld, int rows, int I, int kind, float limit, float alpha, int paired) {
@@ -572,6 +573,8 @@ __global__ void gated_act_kernel(const IT* __restrict__ in, int n_in, size_t in_
         float v;
         if (kind == 0) {
             v = g / (1.f + expf(-g)) * u;
+        } else if (kind == 2) {
+            v = gelu_tanh(g) * u;
         } else {
             g = fminf(g, limit);
             u = fminf(fmaxf(u, -limit), limit);
@@ -585,7 +588,7 @@ extern "C" int rb_gated_act(const void* in, int in_dtype, int n_in, long long in
                             int out_dtype, long long out_ld, int rows, int I, int kind, float limit, float alpha,
                             int paired, void* stream) {
     if (rows <= 0 || I <= 0) return RB_OK;
-    if (n_in < 1 || kind < 0 || kind > 1 || (paired && I % 16)) return RB_ERR_BAD_SIZE;
+    if (n_in < 1 || kind < 0 || kind > 2 || (paired && I % 16)) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t n = (size_t)rows * I;
     const int threads = 256;
@@ -601,6 +604,46 @@ extern "C" int rb_gated_act(const void* in, int in_dtype, int n_in, long long in
     else if (in_dtype == RB_F32 && out_dtype == RB_F32)
         RB_LAUNCH((gated_act_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, n_in, (size_t)in_stride,
                   (size_t)in_ld, (float*)out, (size_t)out_ld, rows, I, kind, limit, alpha, paired);
+    else
+        return RB_ERR_BAD_DTYPE;
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// ---- heads of an attention result times a gate a head, narrowed to the values' width ------------------------
+// in [T, heads, in_w] -> out [T, heads, out_w] (out_w <= in_w: what lies beyond is padding), each head of a token
+// multiplied by gate[t, head] (float32; absent: 1).  The product is formed in 32-bit.
+template <typename AT>
+__global__ void head_gate_kernel(const AT* __restrict__ in, long long ld_in, int in_w, AT* __restrict__ out, long long ld_out,
+                                 int out_w, const float* __restrict__ gate, int heads, int T) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t n = (size_t)T * heads * out_w;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t th = idx / out_w;
+        const int d = (int)(idx - th * out_w);
+        const size_t t = th / heads;
+        const int h = (int)(th - t * heads);
+        const float g = gate ? gate[th] : 1.f;
+        out[t * ld_out + (size_t)h * out_w + d] = from_f32<AT>(to_f32(in[t * ld_in + (size_t)h * in_w + d]) * g);
+    }
+}
+
+extern "C" int rb_head_gate(const void* in, long long ld_in, int in_w, void* out, long long ld_out, int out_w,
+                            const float* gate, int heads, int T, int dtype, void* stream) {
+    if (T <= 0 || heads <= 0) return RB_OK;
+    if (out_w <= 0 || out_w > in_w) return RB_ERR_BAD_SIZE;
+    const size_t n = (size_t)T * heads * out_w;
+    const int threads = 256;
+    const size_t want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RB_BF16)
+        RB_LAUNCH((head_gate_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)in, ld_in, in_w,
+                  (__nv_bfloat16*)out, ld_out, out_w, gate, heads, T);
+    else if (dtype == RB_F32)
+        RB_LAUNCH((head_gate_kernel<float>), dim3(blocks), dim3(threads), 0, s, (const float*)in, ld_in, in_w, (float*)out,
+                  ld_out, out_w, gate, heads, T);
     else
         return RB_ERR_BAD_DTYPE;
     RB_LAUNCH_CHECK();

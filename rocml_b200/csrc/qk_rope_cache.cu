@@ -10,6 +10,12 @@
 // Rotation (rocml-kernels/kernels/rope.hip:18-33): for i < rot/2, a = pos * inv_freq[i],
 // (x_i, x_{i+rot/2}) <- (x_i cos a - x_{i+rot/2} sin a, x_i sin a + x_{i+rot/2} cos a).
 // inv_freq comes from the position-encoding part, so another encoding only changes the table.
+// With `interleaved` the pairs are neighbours instead: (x_2i, x_2i+1) turn by the same angle i.
+//
+// The general kernel also takes value heads of another width than the key heads (`vd`), writes every
+// head `hdp` wide (zeros beyond its own width: queries and keys padded with zeros score the same, and
+// padded values give zeros that the consumer drops), so that one attention kernel with one head size
+// serves them, and turns `n_gate` more columns of the row into sigmoid gates (32-bit).
 #include "common.cuh"
 #include "api.h"
 
@@ -27,14 +33,16 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
                                           const int* __restrict__ slot_of_token,
                                           const int* __restrict__ block_table, int max_pages,
                                           AT* __restrict__ k_cache, AT* __restrict__ v_cache, int write_kv,
-                                          const float2* __restrict__ cs_table) {
+                                          const float2* __restrict__ cs_table, int vd, int hdp, int interleaved,
+                                          int n_gate, float* __restrict__ gate_out) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* buf = smem + (size_t)warp * hd;
-    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    float* buf = smem + (size_t)warp * hdp;
+    const int kv_heads = write_kv ? 2 * nkv : 0;
+    const int heads_total = nq + kv_heads + (n_gate > 0 ? 1 : 0);
     const long long item = (long long)blockIdx.x * warps_per_block + warp;
     if (item >= (long long)T * heads_total) return;
     const int t = (int)(item / heads_total);
@@ -43,25 +51,37 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
     if (slot < 0) return;  // padding
     const int pos = positions[t];
 
+    if (h >= nq + kv_heads) {
+        // the gates: the row's last n_gate columns, sigmoid in 32-bit
+        const IT* g = in + (size_t)t * row_stride + (size_t)nq * hd + (write_kv ? (size_t)nkv * (hd + vd) : 0);
+        for (int i = lane; i < n_gate; i += 32) {
+            float v = 0.f;
+            for (int s = 0; s < n_in; ++s) v += to_f32(g[(size_t)s * in_stride + i]);
+            gate_out[(size_t)t * n_gate + i] = 1.f / (1.f + expf(-v));
+        }
+        return;
+    }
     int kind, head;  // 0 q, 1 k, 2 v
     if (h < nq) { kind = 0; head = h; }
     else if (h < nq + nkv) { kind = 1; head = h - nq; }
     else { kind = 2; head = h - nq - nkv; }
-    const IT* src = in + (size_t)t * row_stride + (size_t)h * hd;
+    const IT* src = in + (size_t)t * row_stride + (kind == 2 ? (size_t)(nq + nkv) * hd + (size_t)head * vd : (size_t)h * hd);
+    if (kind == 2) hd = vd;     // from here on: the width of this head in the row
 
     AT* dst;
     if (kind == 0) {
-        dst = q_out + (size_t)t * q_stride + (size_t)head * hd;
+        dst = q_out + (size_t)t * q_stride + (size_t)head * hdp;
     } else {
         const int page = block_table[(size_t)slot * max_pages + (pos / RB_PAGE)];
         if (page < 0) return;  // no page: the host never schedules this; skip rather than fault
         AT* base = (kind == 1 ? k_cache : v_cache);
-        dst = base + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hd;
+        dst = base + (((size_t)page * nkv + head) * RB_PAGE + (pos % RB_PAGE)) * hdp;
     }
+    for (int i = hd + lane; i < hdp; i += 32) dst[i] = from_f32<AT>(0.f);
 
     float ss = 0.f;
     if (n_in > 1 && sizeof(IT) == 4 && (hd & 3) == 0 && (in_stride & 3) == 0 && (row_stride & 3) == 0 &&
-        ((uintptr_t)in & 15) == 0) {
+        ((uintptr_t)src & 15) == 0) {
         // partial sums in float32: 16-byte loads, four partial sums in flight, added in order
         const float4* s4 = reinterpret_cast<const float4*>(src);
         const size_t st4 = in_stride >> 2;
@@ -101,13 +121,14 @@ __global__ void qk_norm_rope_cache_kernel(const IT* __restrict__ in, int n_in, s
     const float inv = w ? rsqrtf(ss / (float)hd + eps) : 1.f;
     const int half = inv_freq ? rot_dim / 2 : 0;
     for (int i = lane; i < half; i += 32) {
-        float x0 = buf[i], x1 = buf[i + half];
-        if (w) { x0 = x0 * inv * to_f32(w[i]); x1 = x1 * inv * to_f32(w[i + half]); }
+        const int i0 = interleaved ? 2 * i : i, i1 = interleaved ? 2 * i + 1 : i + half;
+        float x0 = buf[i0], x1 = buf[i1];
+        if (w) { x0 = x0 * inv * to_f32(w[i0]); x1 = x1 * inv * to_f32(w[i1]); }
         float sn, cs;
         if (cs_table) { const float2 c2 = cs_table[(size_t)t * half + i]; cs = c2.x; sn = c2.y; }
         else sincosf((float)pos * inv_freq[i], &sn, &cs);
-        dst[i] = from_f32<AT>(x0 * cs - x1 * sn);
-        dst[i + half] = from_f32<AT>(x0 * sn + x1 * cs);
+        dst[i0] = from_f32<AT>(x0 * cs - x1 * sn);
+        dst[i1] = from_f32<AT>(x0 * sn + x1 * cs);
     }
     for (int i = 2 * half + lane; i < hd; i += 32) {
         float x = buf[i];
@@ -267,13 +288,14 @@ static int launch_qk(const void* in, int n_in, long long in_stride, int row_stri
                      int T, int nq, int nkv, int hd, const void* qw, const void* kw, float eps,
                      const float* inv_freq, int rot_dim, const int* positions, const int* slot_of_token,
                      const int* block_table, int max_pages, void* k_cache, void* v_cache, int write_kv,
-                     const float2* cs_table, cudaStream_t s) {
+                     const float2* cs_table, int vd, int hdp, int interleaved, int n_gate, float* gate_out, cudaStream_t s) {
     const int warps = 4;
-    const long long items = (long long)T * (nq + (write_kv ? 2 * nkv : 0));
+    const long long items = (long long)T * (nq + (write_kv ? 2 * nkv : 0) + (n_gate > 0 ? 1 : 0));
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 0x7fffffffLL) return RB_ERR_BAD_SIZE;
     const size_t esz = sizeof(IT);
-    if (hd == 128 && (!inv_freq || rot_dim == 128) && (((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)k_cache |
+    if (hd == 128 && vd == 128 && hdp == 128 && n_gate == 0 && !(inv_freq && interleaved) &&
+        (!inv_freq || rot_dim == 128) && (((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)k_cache |
                                                         (uintptr_t)v_cache | (uintptr_t)qw | (uintptr_t)kw |
                                                         (uintptr_t)cs_table) & 15) == 0 &&
         (row_stride * esz) % 16 == 0 && ((size_t)in_stride * esz) % 16 == 0 && (q_stride * sizeof(AT)) % 16 == 0) {
@@ -284,12 +306,12 @@ static int launch_qk(const void* in, int n_in, long long in_stride, int row_stri
                   cs_table);
         return RB_OK;
     }
-    const size_t smem = (size_t)warps * hd * sizeof(float);
+    const size_t smem = (size_t)warps * hdp * sizeof(float);
     if (smem > 48 * 1024) return RB_ERR_BAD_SIZE;
     RB_LAUNCH((qk_norm_rope_cache_kernel<IT, AT, WT>), dim3((int)blocks), dim3(warps * 32), smem, s, (const IT*)in,
               n_in, (size_t)in_stride, row_stride, (AT*)q_out, q_stride, T, nq, nkv, hd, (const WT*)qw,
               (const WT*)kw, eps, inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages,
-              (AT*)k_cache, (AT*)v_cache, write_kv, cs_table);
+              (AT*)k_cache, (AT*)v_cache, write_kv, cs_table, vd, hdp, interleaved, n_gate, gate_out);
     return RB_OK;
 }
 
@@ -298,15 +320,19 @@ extern "C" int rb_qk_norm_rope_cache(const void* in, int in_dtype, int n_in, lon
                                      const void* q_norm_w, const void* k_norm_w, int w_dtype, float eps,
                                      const float* inv_freq, int rot_dim, const int* positions,
                                      const int* slot_of_token, const int* block_table, int max_pages,
-                                     void* k_cache, void* v_cache, int write_kv, const void* cos_sin, void* stream) {
+                                     void* k_cache, void* v_cache, int write_kv, const void* cos_sin, int vd, int hdp,
+                                     int interleaved, int n_gate, float* gate_out, void* stream) {
     if (T <= 0) return RB_OK;
-    if (hd <= 0 || hd % 2 || n_in < 1 || (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > hd)))
+    if (vd <= 0) vd = hd;
+    if (hdp <= 0) hdp = hd > vd ? hd : vd;
+    if (hd <= 0 || n_in < 1 || hdp < hd || hdp < vd || (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > hd)) ||
+        n_gate < 0 || (n_gate > 0 && !gate_out) || ((q_norm_w || k_norm_w) && vd != hd))
         return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
 #define RB_QK_ARGS in, n_in, in_stride, row_stride, q_out, q_stride, T, nq, nkv, hd, q_norm_w, k_norm_w, eps, \
                    inv_freq, rot_dim, positions, slot_of_token, block_table, max_pages, k_cache, v_cache, write_kv, \
-                   (const float2*)cos_sin, s
+                   (const float2*)cos_sin, vd, hdp, interleaved, n_gate, gate_out, s
     if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<bf, bf, bf>(RB_QK_ARGS);
     if (in_dtype == RB_BF16 && act_dtype == RB_BF16 && w_dtype == RB_F32) return launch_qk<bf, bf, float>(RB_QK_ARGS);
     if (in_dtype == RB_F32 && act_dtype == RB_BF16 && w_dtype == RB_BF16) return launch_qk<float, bf, bf>(RB_QK_ARGS);

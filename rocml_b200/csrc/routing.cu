@@ -5,10 +5,15 @@
 //            bias, not renormalised).  Each choice also takes the next free place among its expert's rows
 //            (an atomic counter: the order of an expert's rows is arbitrary, and no result depends on it,
 //            because every row is computed by itself).  Padding tokens (slot -1) choose nothing.
+//            With `n_groups` > 1 the experts form that many equal groups of neighbours; a group's score is the
+//            sum of its two largest s_e + bias_e (of its only one, in groups of one), and only experts of the
+//            `keep_groups` best groups (ties: the lower number) can be chosen.  With `renormalize` the weights
+//            are divided by their sum + norm_eps.
 //   plan     one block: every expert's rows start at a multiple of `tile_rows`; tile i of the row buffer
 //            belongs to expert tile_group[i] (-1: unused).
 //   gather   a token's normalised row is copied to each of its `top` places; row_of[t, j] names the place.
-//   combine  out[t] = sum_j weight[t, j] * y[row_of[t, j]] in 32-bit, j ascending.
+//   combine  out[t] = sum_j weight[t, j] * y[row_of[t, j]] in 32-bit, j ascending; optionally plus
+//            sigmoid(extra_gate[t]) * (sum of the partial sums extra[s][t]): an expert that every token uses.
 #include "common.cuh"
 #include "api.h"
 
@@ -121,9 +126,10 @@ template <typename BT>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int ldz, const BT* __restrict__ bias, const int* __restrict__ slot_of_token,
                  int T, int E, int top, int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ place,
-                 int* __restrict__ counts) {
+                 int* __restrict__ counts, int n_groups, int keep_groups, int renormalize, float norm_eps) {
     pdl_trigger();
     pdl_wait();
+    extern __shared__ float route_s[];           // [warps][E + n_groups] when groups are cut, else unused
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (t >= T) return;
@@ -143,6 +149,46 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const BT* __restrict__ bi
             c[i] = -INFINITY;
         }
     }
+    if (n_groups > 1 && keep_groups < n_groups) {
+        // the groups' cut: scores to shared memory, a lane scores whole groups, the best groups are marked
+        float* cs = route_s + (size_t)(threadIdx.x >> 5) * (E + n_groups);
+        float* gs = cs + E;
+        const int per = E / n_groups;
+#pragma unroll
+        for (int i = 0; i < MAX_EPL; ++i)
+            if (lane + i * 32 < E) cs[lane + i * 32] = c[i];
+        __syncwarp();
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;       // the two largest
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = cs[e];
+                if (v > a) { b = a; a = v; } else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        for (int j = 0; j < keep_groups; ++j) {
+            float best = -INFINITY;
+            int best_g = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32)
+                if (gs[g] > best) { best = gs[g]; best_g = g; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+            }
+            __syncwarp();
+            if (lane == 0 && best_g < n_groups) gs[best_g] = -INFINITY;     // kept: marked by -inf, not NaN
+            __syncwarp();
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_EPL; ++i) {
+            const int e = lane + i * 32;
+            if (e < E && gs[e / per] != -INFINITY) c[i] = -INFINITY;       // its group was not kept
+        }
+    }
+    float picked_sum = 0.f;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY, best_s = 0.f;
         int best_e = 0x7fffffff;
@@ -162,11 +208,16 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const BT* __restrict__ bi
         for (int i = 0; i < MAX_EPL; ++i)
             if (lane + i * 32 == best_e) c[i] = -INFINITY;
         if (best_e >= E) best_e = E - 1;      // scores that compare with nothing (NaN): stay inside the tables
+        picked_sum += best_s;
         if (lane == 0) {
             ids[(size_t)t * top + j] = best_e;
             weights[(size_t)t * top + j] = best_s;
             place[(size_t)t * top + j] = atomicAdd(&counts[best_e], 1);
         }
+    }
+    if (renormalize && lane == 0) {
+        const float d = picked_sum + norm_eps;
+        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= d;
     }
 }
 
@@ -216,15 +267,22 @@ moe_gather_kernel(const AT* __restrict__ x, int H, const int* __restrict__ ids, 
 
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, long long ldy, const int* __restrict__ row_of, const float* __restrict__ weights,
-                   int top, float* __restrict__ out, int H) {
+                   int top, float* __restrict__ out, int H, const float* __restrict__ extra, int n_extra,
+                   long long extra_stride, const float* __restrict__ extra_gate, int extra_gate_ld) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
+    const float eg = extra ? (extra_gate ? 1.f / (1.f + expf(-extra_gate[(size_t)t * extra_gate_ld])) : 1.f) : 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = 0.f;
         for (int j = 0; j < top; ++j) {
             const int r = row_of[(size_t)t * top + j];
             if (r >= 0) v = fmaf(weights[(size_t)t * top + j], y[(size_t)r * ldy + i], v);
+        }
+        if (extra) {
+            float x = 0.f;
+            for (int s = 0; s < n_extra; ++s) x += extra[(size_t)s * extra_stride + (size_t)t * H + i];
+            v = fmaf(eg, x, v);
         }
         out[(size_t)t * H + i] = v;
     }
@@ -254,18 +312,23 @@ extern "C" int rb_router_logits(const void* x, int x_dtype, long long ldx, const
 }
 
 extern "C" int rb_moe_route(const float* z, int ldz, const void* bias, int bias_dtype, const int* slot_of_token, int T,
-                            int E, int top, int* ids, float* weights, int* place, int* counts, void* stream) {
+                            int E, int top, int* ids, float* weights, int* place, int* counts, int n_groups,
+                            int keep_groups, int renormalize, float norm_eps, void* stream) {
     if (T <= 0) return RB_OK;
     if (E <= 0 || E > 32 * MAX_EPL || top <= 0 || top > E) return RB_ERR_BAD_SIZE;
+    if (n_groups < 1) n_groups = 1;
+    if (keep_groups < 1 || keep_groups > n_groups) keep_groups = n_groups;
+    if (E % n_groups || (long long)keep_groups * (E / n_groups) < top) return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int warps = 4;
     dim3 grid((T + warps - 1) / warps);
+    const size_t smem = (n_groups > 1 && keep_groups < n_groups) ? (size_t)warps * (E + n_groups) * sizeof(float) : 0;
     if (!bias || bias_dtype == RB_F32)
-        RB_LAUNCH((moe_route_kernel<float>), grid, dim3(warps * 32), 0, s, z, ldz, (const float*)bias, slot_of_token, T, E, top,
-                  ids, weights, place, counts);
+        RB_LAUNCH((moe_route_kernel<float>), grid, dim3(warps * 32), smem, s, z, ldz, (const float*)bias, slot_of_token, T, E, top,
+                  ids, weights, place, counts, n_groups, keep_groups, renormalize, norm_eps);
     else if (bias_dtype == RB_BF16)
-        RB_LAUNCH((moe_route_kernel<__nv_bfloat16>), grid, dim3(warps * 32), 0, s, z, ldz, (const __nv_bfloat16*)bias,
-                  slot_of_token, T, E, top, ids, weights, place, counts);
+        RB_LAUNCH((moe_route_kernel<__nv_bfloat16>), grid, dim3(warps * 32), smem, s, z, ldz, (const __nv_bfloat16*)bias,
+                  slot_of_token, T, E, top, ids, weights, place, counts, n_groups, keep_groups, renormalize, norm_eps);
     else
         return RB_ERR_BAD_DTYPE;
     RB_LAUNCH_CHECK();
@@ -297,9 +360,11 @@ extern "C" int rb_moe_gather(const void* x, int dtype, int H, const int* ids, co
 }
 
 extern "C" int rb_moe_combine(const float* y, long long ldy, const int* row_of, const float* weights, int T, int top,
-                              float* out, int H, void* stream) {
+                              float* out, int H, const float* extra, int n_extra, long long extra_stride,
+                              const float* extra_gate, int extra_gate_ld, void* stream) {
     if (T <= 0) return RB_OK;
-    RB_LAUNCH((moe_combine_kernel), dim3(T), dim3(256), 0, (cudaStream_t)stream, y, ldy, row_of, weights, top, out, H);
+    RB_LAUNCH((moe_combine_kernel), dim3(T), dim3(256), 0, (cudaStream_t)stream, y, ldy, row_of, weights, top, out, H,
+              extra, n_extra, extra_stride, extra_gate, extra_gate_ld);
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

@@ -130,7 +130,7 @@ def _lib():
         lib.rb_silu_mul.argtypes = [_vp, _i, _i, _ll, _vp, _i, _i, _i, _i, _vp]
         lib.rb_cast.argtypes = [_vp, _i, _vp, _i, _ll, _vp]
         lib.rb_qk_norm_rope_cache.argtypes = [_vp, _i, _i, _ll, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f,
-                                              _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp]
+                                              _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp]
         lib.rb_rope_table.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
         lib.rb_gemm_generic.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _ll, _vp]
         lib.rb_attention_generic.argtypes = [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i,
@@ -164,12 +164,17 @@ def _lib():
         lib.rb_scale.argtypes = [_vp, _ll, _f, _vp]
         lib.rb_latent_prep.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _vp, _i, _f, _vp, _i, _vp, _vp, _i, _vp, _vp,
                                        _vp, _i, _i, _vp]
-        lib.rb_moe_route.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
+        lib.rb_moe_route.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]
         lib.rb_moe_plan.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp]
         lib.rb_moe_gather.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]
-        lib.rb_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _i, _vp]
+        lib.rb_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _ll, _vp, _i, _vp]
         lib.rb_grouped_matmul.argtypes = [_vp, _i, _ll, _i, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _vp, _i,
                                           _vp, _i, _i, _f, _f, _vp]
+        lib.rb_head_gate.argtypes = [_vp, _ll, _i, _vp, _ll, _i, _vp, _i, _i, _i, _vp]
+        lib.rb_decay_scan.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _i,
+                                      _vp, _i, _vp]
+        lib.rb_group_norm_gate.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _i, _f, _i, _i, _i, _vp, _i, _i, _vp,
+                                           _i, _vp]
         lib.rb_gemm_tcgen05_set_wait.argtypes = [_ll, _i]
         lib.rb_gemm_tcgen05_set_wait.restype = None
         _sigs_done = True
@@ -260,17 +265,29 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, n
                        inv_freq: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
                        slot_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], write_kv: bool = True,
-                       cos_sin: Optional[torch.Tensor] = None):
+                       cos_sin: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
+                       padded_head_dim: Optional[int] = None, interleaved: bool = False,
+                       gates: Optional[torch.Tensor] = None):
     """``cos_sin`` (from rope_table, float32 [T, rot_dim / 2, 2]) replaces the kernel's own sincosf.
-    proj [T, nq*hd (+ 2*nkv*hd)] (or [S, T, ...] partial sums): q normalised and rotated into q_out
-    (rows of nq*hd, any row stride; it may be ``proj`` itself); k (normalised, rotated) and v written
-    to their pages."""
-    width = (nq + (2 * nkv if write_kv else 0)) * hd
+    proj [T, nq*hd (+ nkv*hd + nkv*vd) (+ gates)] (or [S, T, ...] partial sums): q normalised and rotated into
+    q_out (rows of nq*hdp, any row stride; it may be ``proj`` itself when nothing is padded); k (normalised,
+    rotated) and v written to their pages.  ``v_head_dim`` (vd): the value heads' width when it is not hd;
+    ``padded_head_dim`` (hdp): the width of every head in q_out and in the cache (zeros beyond a head's own);
+    ``interleaved``: rotation pairs are neighbours (2i, 2i + 1) instead of (i, i + rot_dim / 2); ``gates``
+    (float32 [T, n]): the sigmoid of the row's last n columns."""
+    vd = hd if v_head_dim is None else int(v_head_dim)
+    hdp = max(hd, vd) if padded_head_dim is None else int(padded_head_dim)
+    n_gate = 0 if gates is None else gates.shape[-1]
+    width = nq * hd + (nkv * (hd + vd) if write_kv else 0)
     n_in, in_stride, row_stride = _partials(proj, "qk_norm_rope_cache")
-    if proj.shape[-1] != width:
-        raise KernelError(f"qk_norm_rope_cache: projections must be {width} wide")
-    if q_out.stride(-1) != 1 or q_out.shape[-1] < nq * hd:
-        raise KernelError("qk_norm_rope_cache: q_out rows must hold nq * hd elements with unit stride")
+    if proj.shape[-1] < width + n_gate or (n_gate == 0 and hdp == hd and proj.shape[-1] != width):
+        raise KernelError(f"qk_norm_rope_cache: projections must be {width + n_gate} wide")
+    if gates is not None and (gates.dtype != torch.float32 or not gates.is_contiguous() or gates.shape[0] < n_tokens):
+        raise KernelError("qk_norm_rope_cache: gates must be contiguous float32 [T, n]")
+    if q_out.stride(-1) != 1 or q_out.shape[-1] < nq * hdp:
+        raise KernelError("qk_norm_rope_cache: q_out rows must hold nq * hdp elements with unit stride")
+    if hdp != hd and q_out.data_ptr() == proj.data_ptr():
+        raise KernelError("qk_norm_rope_cache: padded heads cannot be written over the projections")
     if (q_norm_w is None) != (k_norm_w is None):
         raise KernelError("qk_norm_rope_cache: give both norm weights or neither")
     wd = dtype_code(q_norm_w.dtype) if q_norm_w is not None else F32
@@ -282,15 +299,15 @@ def qk_norm_rope_cache(proj: torch.Tensor, q_out: torch.Tensor, n_tokens: int, n
         if k_cache is None or v_cache is None or block_table is None:
             raise KernelError("qk_norm_rope_cache: cache tensors missing")
         if k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype or not k_cache.is_contiguous() or \
-                tuple(k_cache.shape[1:]) != (nkv, PAGE, hd):
-            raise KernelError("qk_norm_rope_cache: cache must be [pages, nkv, 64, hd] of the activations' type")
+                tuple(k_cache.shape[1:]) != (nkv, PAGE, hdp):
+            raise KernelError("qk_norm_rope_cache: cache must be [pages, nkv, 64, hdp] of the activations' type")
     max_pages = block_table.shape[1] if block_table is not None else 0
     rc = _lib().rb_qk_norm_rope_cache(
         _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, _ptr(q_out), dtype_code(q_out.dtype),
         q_out.stride(-2), n_tokens, nq, nkv, hd, _ptr(q_norm_w), _ptr(k_norm_w), wd, float(eps), _ptr(inv_freq),
         rot_dim, _i32(positions, "positions"), _i32(slot_of_token, "slot_of_token"),
         None if block_table is None else _i32(block_table, "block_table"), max_pages, _ptr(k_cache), _ptr(v_cache),
-        1 if write_kv else 0, _ptr(cos_sin), _stream())
+        1 if write_kv else 0, _ptr(cos_sin), vd, hdp, 1 if interleaved else 0, n_gate, _ptr(gates), _stream())
     _check(rc, "qk_norm_rope_cache")
 
 
@@ -363,7 +380,7 @@ def prefill_heads_first(n_seqs: int, nkv: int, hd: int, max_kv_len: int, window:
     runs one head after another (the blocks that run together share keys and values): the first while
     the bfloat16 keys and values of the step's contexts fit the L2 cache (measured: 26 % faster at 2,048
     tokens, 6 % at 16,384, 6 % slower at 32,768, where 134 MB are read by every query tile)."""
-    span = min(max_kv_len, window) if window and window > 0 else max_kv_len
+    span = min(max_kv_len, abs(window)) if window else max_kv_len      # a window, or blocks of -window positions
     return n_seqs * nkv * span * hd * 4 <= PREFILL_L2_BYTES
 
 
@@ -918,7 +935,7 @@ def postnorm_add_norm(resid: torch.Tensor, delta: torch.Tensor, w_post: torch.Te
     _check(rc, "postnorm_add_norm")
 
 
-GATED_ACTS = {"silu": 0, "clamped_swish": 1}
+GATED_ACTS = {"silu": 0, "clamped_swish": 1, "gelu_tanh": 2}
 
 
 @_profiled(lambda a, facts: _cost.silu_mul(a["out"].shape[0] if a["rows"] is None else a["rows"], a["out"].shape[1],
@@ -996,11 +1013,17 @@ def router_logits(x: torch.Tensor, w: torch.Tensor, z: torch.Tensor, n_tokens: i
 
 @_profiled(lambda a, facts: (a["n_tokens"] * (a["z"].shape[1] * 4 + a["top"] * 12), a["n_tokens"] * a["z"].shape[1] * 8))
 def moe_route(z: torch.Tensor, bias: Optional[torch.Tensor], slot_of_token: torch.Tensor, n_tokens: int, top: int,
-              ids: torch.Tensor, weights: torch.Tensor, place: torch.Tensor, counts: torch.Tensor):
-    """z float32 [T, E] router logits -> per token the ``top`` experts by sigmoid(z) + bias (``ids`` int32 [T, top],
+              ids: torch.Tensor, weights: torch.Tensor, place: torch.Tensor, counts: torch.Tensor,
+              n_groups: int = 1, keep_groups: int = 1, renormalize: bool = False, norm_eps: float = 0.0):
+    """z float32 [T, >= E] router logits -> per token the ``top`` experts by sigmoid(z) + bias (``ids`` int32 [T, top],
     -1 for padding tokens), their weights sigmoid(z) (float32 [T, top]) and each choice's place among its expert's
-    rows (``place``); ``counts`` int32 [E], zero on entry, ends as the rows of every expert."""
-    E = z.shape[1]
+    rows (``place``); ``counts`` int32 [E], zero on entry, ends as the rows of every expert (E is its length; z may
+    have more columns).  ``n_groups`` > 1: the experts form equal groups of neighbours, a group's score is the sum of
+    its two largest scores, and only experts of the ``keep_groups`` best groups can be chosen.  ``renormalize``: the
+    weights are divided by their sum + ``norm_eps``."""
+    E = counts.numel()
+    if z.shape[1] < E:
+        raise KernelError("moe_route: fewer router logits than experts")
     if z.dtype != torch.float32 or z.stride(1) != 1:
         raise KernelError("moe_route: router logits must be float32 with unit inner stride")
     for t, name in ((ids, "ids"), (place, "place")):
@@ -1012,7 +1035,8 @@ def moe_route(z: torch.Tensor, bias: Optional[torch.Tensor], slot_of_token: torc
         raise KernelError("moe_route: counts (int32) and bias must be [E]")
     rc = _lib().rb_moe_route(_ptr(z), z.stride(0), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
                              _i32(slot_of_token, "slot_of_token"), n_tokens, E, top, _ptr(ids), _ptr(weights),
-                             _ptr(place), _ptr(counts), _stream())
+                             _ptr(place), _ptr(counts), int(n_groups), int(keep_groups), 1 if renormalize else 0,
+                             float(norm_eps), _stream())
     _check(rc, "moe_route")
 
 
@@ -1039,13 +1063,90 @@ def moe_gather(x: torch.Tensor, ids: torch.Tensor, place: torch.Tensor, starts: 
 
 
 @_profiled(lambda a, facts: (a["n_tokens"] * a["out"].shape[1] * 4 * (1 + a["top"]), a["n_tokens"] * a["out"].shape[1] * 2 * a["top"]))
-def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, n_tokens: int, top: int, out: torch.Tensor):
-    """out [T, H] float32 = sum over a token's choices j of weights[t, j] * y[row_of[t, j]] (y float32 [R, H])."""
+def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, n_tokens: int, top: int, out: torch.Tensor,
+                extra: Optional[torch.Tensor] = None, extra_gate: Optional[torch.Tensor] = None):
+    """out [T, H] float32 = sum over a token's choices j of weights[t, j] * y[row_of[t, j]] (y float32 [R, H]), plus,
+    with ``extra`` (float32 [S, T, H] partial sums), sigmoid(extra_gate[t]) * sum_s extra[s, t] (``extra_gate``: a
+    float32 column, one logit a token, any row stride; None: no gate)."""
     if y.dtype != torch.float32 or out.dtype != torch.float32 or y.stride(1) != 1 or not out.is_contiguous() or \
             y.shape[1] != out.shape[1]:
         raise KernelError("moe_combine: y and out must be float32 of one width")
+    n_extra = stride = gate_ld = 0
+    if extra is not None:
+        if extra.dtype != torch.float32 or extra.dim() != 3 or extra.shape[2] != out.shape[1] or extra.shape[1] < n_tokens \
+                or extra.stride(2) != 1 or extra.stride(1) != out.shape[1]:
+            raise KernelError("moe_combine: extra must be float32 [S, T, H] with dense rows")
+        n_extra, stride = extra.shape[0], extra.stride(0)
+        if extra_gate is not None:
+            if extra_gate.dtype != torch.float32 or extra_gate.dim() != 1 or extra_gate.shape[0] < n_tokens:
+                raise KernelError("moe_combine: extra_gate must be a float32 column of T logits")
+            gate_ld = extra_gate.stride(0)
     _check(_lib().rb_moe_combine(_ptr(y), y.stride(0), _ptr(row_of), _ptr(weights), n_tokens, top, _ptr(out),
-                                 out.shape[1], _stream()), "moe_combine")
+                                 out.shape[1], _ptr(extra), n_extra, stride,
+                                 _ptr(extra_gate) if extra is not None else None, gate_ld, _stream()), "moe_combine")
+
+
+# ---- linear attention with a fixed decay per head ------------------------------------------------------------------
+
+UNIT_ACTS = {"none": 0, "silu": 1, "sigmoid": 2}
+
+
+@_profiled(lambda a, facts: _cost.decay_scan(a["n_tokens"], a["n_seqs"], a["heads"], a["dim"], a["vdim"], _n_in(a["proj"]),
+                                             _esz(a["proj"])))
+def decay_scan(proj: torch.Tensor, n_tokens: int, q_off: int, k_off: int, v_off: int, heads: int, dim: int, vdim: int,
+               qk_act: str, v_act: str, k_scale: float, decay: torch.Tensor, state: torch.Tensor, seq_slot: torch.Tensor,
+               cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor):
+    """The step's tokens through S = decay[h] * S + k v^T, o = S^T q for every (sequence, head).  ``proj`` [T, N] (or
+    [S, T, N] float32 partial sums) holds q and k (heads * dim columns from q_off and k_off) and v (heads * vdim from
+    v_off); ``qk_act`` / ``v_act``: "none" or "silu"; k is multiplied by ``k_scale``.  ``state`` float32
+    [slots, heads, dim, vdim] is read and written in place for the slots of ``seq_slot``; ``out`` float32
+    [T, heads * vdim]."""
+    n_in, in_stride, row_stride = _partials(proj, "decay_scan")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError("decay_scan: state must be contiguous float32 [slots, heads, dim, vdim]")
+    if decay.dtype != torch.float32 or decay.numel() != heads or not decay.is_contiguous():
+        raise KernelError("decay_scan: decay must be float32 [heads]")
+    if out.dtype != torch.float32 or out.stride(-1) != 1 or out.shape[-1] != heads * vdim or out.shape[0] < n_tokens:
+        raise KernelError("decay_scan: out must be float32 [T, heads * vdim]")
+    if max(q_off, k_off) + heads * dim > proj.shape[-1] or v_off + heads * vdim > proj.shape[-1]:
+        raise KernelError("decay_scan: the projection rows are too narrow")
+    rc = _lib().rb_decay_scan(_ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, q_off, k_off, v_off, heads,
+                              dim, vdim, UNIT_ACTS[qk_act], UNIT_ACTS[v_act], float(k_scale), _ptr(decay), _ptr(state),
+                              _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), n_seqs, _ptr(out), out.stride(0), _stream())
+    _check(rc, "decay_scan")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["o"].shape[1] * (4 + _esz(a["proj"]) * _n_in(a["proj"]) + _esz(a["out"])),
+                             a["n_tokens"] * a["o"].shape[1] * 8))
+def group_norm_gate(o: torch.Tensor, proj: torch.Tensor, g_off: int, weight: Optional[torch.Tensor], eps: float, groups: int,
+                    gate_act: str, out: torch.Tensor, slot_of_token: torch.Tensor, n_tokens: int):
+    """out [T, W] = o / rms(o over each of ``groups`` equal column groups, eps inside the root) (* weight [W]) *
+    act(gate), the gate being columns g_off .. g_off + W of ``proj`` (partial sums added first); ``gate_act`` "none",
+    "silu" or "sigmoid".  o float32; out in the activations' type."""
+    W = o.shape[1]
+    n_in, in_stride, row_stride = _partials(proj, "group_norm_gate")
+    if o.dtype != torch.float32 or o.stride(1) != 1 or out.stride(1) != 1 or out.shape[1] != W or g_off + W > proj.shape[-1]:
+        raise KernelError("group_norm_gate: o must be float32 [T, W], out [T, W], the gate inside the projection rows")
+    if weight is not None and (weight.numel() != W or not weight.is_contiguous()):
+        raise KernelError("group_norm_gate: the weight must be [W]")
+    rc = _lib().rb_group_norm_gate(_ptr(o), o.stride(0), _ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride,
+                                   g_off, _ptr(weight), dtype_code(weight.dtype) if weight is not None else F32, float(eps),
+                                   groups, W, UNIT_ACTS[gate_act], _ptr(out), dtype_code(out.dtype), out.stride(0),
+                                   _i32(slot_of_token, "slot_of_token"), n_tokens, _stream())
+    _check(rc, "group_norm_gate")
+
+
+@_profiled(lambda a, facts: (a["n_tokens"] * a["heads"] * (a["in_w"] + a["out_w"]) * _esz(a["x"]), a["n_tokens"] * a["heads"] * a["out_w"]))
+def head_gate(x: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], heads: int, in_w: int, out_w: int, n_tokens: int):
+    """out[t, h, :out_w] = x[t, h, :out_w] * gate[t, h]: an attention result's heads (``in_w`` wide, of which
+    ``out_w`` are values and the rest padding) times a float32 gate a head (None: 1)."""
+    if x.dtype != out.dtype or x.stride(-1) != 1 or out.stride(-1) != 1 or x.shape[-1] < heads * in_w or \
+            out.shape[-1] < heads * out_w:
+        raise KernelError("head_gate: shapes or types do not fit")
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.shape[-1] != heads):
+        raise KernelError("head_gate: gate must be contiguous float32 [T, heads]")
+    _check(_lib().rb_head_gate(_ptr(x), x.stride(0), in_w, _ptr(out), out.stride(0), out_w, _ptr(gate), heads, n_tokens,
+                               dtype_code(x.dtype), _stream()), "head_gate")
 
 
 # ---- many small products in one launch ----------------------------------------------------------------------------

@@ -8,16 +8,17 @@ from .base import (
 )
 from .linear import Linear
 from .norm import RMSNorm
-from .position import NoPosition, RotaryNeox, SinusoidPosition
+from .position import NoPosition, RotaryNeox, RotaryPairs, SinusoidPosition
 from .attention import Attention
 from .mlp import GatedMLP
 from .latent_attention import LatentAttention
 from .routed_mlp import RoutedMLP
-from .block import PreNormBlock, SandwichNormBlock
+from .linear_attention import LinearAttention
+from .block import ParallelBlock, PreNormBlock, SandwichNormBlock
 
 __all__ = [
     "BuildEnv", "DeferredNorm", "ResidualSink", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "build_block",
     "build_feed_forward", "build_mixer", "build_norm", "build_position", "register_arrangement",
     "register_feed_forward", "register_mixer", "register_norm", "register_position", "registered",
-    "Linear", "RMSNorm", "NoPosition", "RotaryNeox", "Attention", "GatedMLP", "PreNormBlock", "LatentAttention", "RoutedMLP", "SandwichNormBlock", "SinusoidPosition",
+    "Linear", "RMSNorm", "NoPosition", "RotaryNeox", "Attention", "GatedMLP", "PreNormBlock", "LatentAttention", "RoutedMLP", "SandwichNormBlock", "SinusoidPosition", "RotaryPairs", "LinearAttention", "ParallelBlock",
 ]

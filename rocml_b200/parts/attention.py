@@ -7,7 +7,13 @@ over its sequence's keys at positions <= its own (and inside the window, if the 
 one) -> output projection.  The result is returned as a delta for the residual stream.
 
 Sizes and constants (heads, groups, head size, biases, q/k norm and its eps, window, scale)
-are parameters; a layer that reads another layer's cache projects only q.
+are parameters; a layer that reads another layer's cache projects only q.  Further parameters:
+value heads of another size than the key heads (``v_head_dim``), a mask by blocks of positions
+instead of a window (``chunk``), a sigmoid gate per head on the attention's result, read from the
+layer's input (``gated``), and, through the position encoding, rotation by neighbouring pairs.
+Heads of unequal or odd sizes are written into the cache padded with zeros to one width that the
+attention kernels take: zeros in queries and keys change no score, zeros in values give zeros
+that are dropped before the output projection.
 """
 from __future__ import annotations
 
@@ -33,7 +39,8 @@ PROMPT_FUSED_MIN_TOKENS = 4096
 
 # Tensor-name stems by role, unless the spec's ``names`` says otherwise (the defaults are those of
 # Hugging Face's Qwen3 checkpoints: rocml/src/weights/layer.rs:47-58 lists the same tensors under GGUF names).
-TENSOR_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm"}
+TENSOR_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm",
+                "gate": "gate_proj"}
 
 DECODE_CHUNK = 64   # keys per split of decode attention (one page); fixed, so a row's sums never depend on the batch
 
@@ -51,15 +58,30 @@ class Attention(Mixer):
         self.hd = int(p["head_dim"])
         if self.nq <= 0 or self.nkv <= 0 or self.nq % self.nkv:
             raise ConfigError(f"{self.nq} query heads cannot be grouped over {self.nkv} key/value heads")
-        if self.hd % 16 or self.hd > 256:
-            raise ConfigError(f"head size {self.hd} is not supported: multiples of 16 up to 256")
+        self.vd = int(p.get("v_head_dim") or self.hd)
+        self.gated = bool(p.get("gated", False))
+        self.hdp = -(-max(self.hd, self.vd) // 16) * 16         # the width of every head in the cache
+        if min(self.hd, self.vd) <= 0 or self.hdp > 512:
+            raise ConfigError(f"head sizes {self.hd} (keys) and {self.vd} (values) are not supported: 1 to 512")
         self.bias = bool(p.get("bias", False))
         self.qk_norm = bool(p.get("qk_norm", False))
         self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
         self.window = p.get("window")
+        self.chunk = p.get("chunk")
+        if self.window and self.chunk:
+            raise ConfigError("attention: a layer has a window or blocks of positions, not both")
+        if (self.window is not None and int(self.window) < 1) or (self.chunk is not None and int(self.chunk) < 1):
+            raise ConfigError("attention: a window or a block of positions holds at least one position")
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
         self.shares_cache = bool(p.get("shares_cache", False))  # set by the model for a reading layer
         self.position = build_position(spec.position, self.hd, env)
+        # the plain layout: equal head sizes that the kernels take as they are, rotate-half pairs, no gate
+        self.plain = self.vd == self.hd == self.hdp and not self.gated and \
+            not (self.position.inv_freq is not None and getattr(self.position, "interleaved", False))
+        if not self.plain and self.shares_cache:
+            raise ConfigError("attention: a layer that reads another layer's cache must have the plain layout")
+        if self.qk_norm and self.vd != self.hd:
+            raise ConfigError("attention: q/k norms with value heads of another size are not built")
         qd, kvd = self.nq * self.hd, self.nkv * self.hd
         try:
             self.names = n = tensor_names(p, TENSOR_NAMES)
@@ -68,13 +90,22 @@ class Attention(Mixer):
         if self.shares_cache:
             self.qkv = Linear([n["q"]], [qd], hidden, self.bias, env)
         else:
-            self.qkv = Linear([n["q"], n["k"], n["v"]], [qd, kvd, kvd], hidden, self.bias, env)
-        self.o = Linear([n["o"]], [hidden], qd, self.bias, env)
+            stems, outs = [n["q"], n["k"], n["v"]], [qd, kvd, self.nkv * self.vd]
+            if self.gated:
+                stems, outs = stems + [n["gate"]], outs + [self.nq]
+            self.qkv = Linear(stems, outs, hidden, self.bias, env)
+        self.o = Linear([n["o"]], [hidden], self.nq * self.vd, self.bias, env)
         self.q_norm_w: Optional[torch.Tensor] = None
         self.k_norm_w: Optional[torch.Tensor] = None
 
     def cache_requirement(self):
-        return KVRequirement(self.nkv, self.hd, self.window)
+        return KVRequirement(self.nkv, self.hdp, self.window, chunk=self.chunk)
+
+    def _span(self) -> int:
+        """The mask as the kernels take it: 0 every earlier key, n the last n keys, -n blocks of n positions."""
+        if self.window:
+            return int(self.window)
+        return -int(self.chunk) if self.chunk else 0
 
     def declare(self, prefix: str) -> List[TensorDecl]:
         out = self.qkv.declare(prefix) + self.o.declare(prefix)
@@ -86,6 +117,8 @@ class Attention(Mixer):
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         self.qkv.load(tensors, prefix)
+        if not self.plain:
+            self.qkv.pad_rows(8)     # a stack with a few gate rows is rarely a multiple of 8 wide
         self.o.load(tensors, prefix)
         if self.qk_norm:
             self.q_norm_w = tensors[f"{prefix}{self.names['q_norm']}.weight"]
@@ -100,15 +133,15 @@ class Attention(Mixer):
         """Projections, attention output and the delta (as partial sums: up to 8 of each for few tokens)."""
         esz = 4 if self.env.mode == "float32" else 2
         parts = 8 if n_tokens <= 128 else 1
-        return n_tokens * (self.qkv.n * max(esz, 4 * parts if parts > 1 else esz) + 2 * self.nq * self.hd * esz
-                           + self.hidden * 4 * parts + self.nq * 4 * (self.hd + 2) * (parts if parts > 1 else 0))
+        return n_tokens * (self.qkv.n * max(esz, 4 * parts if parts > 1 else esz) + 3 * self.nq * self.hdp * esz
+                           + self.hidden * 4 * parts + self.nq * 4 * (self.hdp + 2) * (parts if parts > 1 else 0))
 
     def cost(self, q_lens, kv_lens):
         from ..profile import cost as C
         T = sum(q_lens)
         esz = 4 if self.env.mode == "float32" else 2
         parts = [self.qkv.cost(T), self.o.cost(T),
-                 C.attention(q_lens, kv_lens, self.nq, self.nkv, self.hd, esz, int(self.window) if self.window else None)]
+                 C.attention(q_lens, kv_lens, self.nq, self.nkv, self.hdp, esz, self._span() or None)]
         return sum(p[0] for p in parts), sum(p[1] for p in parts)
 
     can_sink = True        # forward() accepts sink=ResidualSink (see parts.base)
@@ -116,7 +149,7 @@ class Attention(Mixer):
     def takes_deferred(self, batch) -> bool:
         """Whether forward() can be handed a DeferredNorm for this step: the decode kernel that takes
         the projections applies the rows' 1/RMS, which a bias inside the projection would spoil."""
-        return (batch.is_decode and self.hd == 128 and not self.bias and self.env.act_dtype == torch.bfloat16
+        return (batch.is_decode and self.plain and self.hd == 128 and not self.bias and self.env.act_dtype == torch.bfloat16
                 and self.qkv.weight is not None and self.qkv.weight.dtype == torch.bfloat16
                 and self.qkv._splits(batch.n_tokens) > 1
                 and (self.shares_cache or self.nq // self.nkv <= 16)     # wider groups: the kernel does not write the cache
@@ -128,9 +161,11 @@ class Attention(Mixer):
         T = batch.n_tokens
         dev, act = self.env.device, self.env.act_dtype
         qd = self.nq * self.hd
-        attn = torch.empty((T, qd), dtype=act, device=dev)
-        window = int(self.window) if self.window else 0
+        window = self._span()
         writes = view.writes and not self.shares_cache
+        if not self.plain:
+            return self._forward_padded(xn, batch, view, window, writes, sink, add_into)
+        attn = torch.empty((T, qd), dtype=act, device=dev)
         done = False
         if isinstance(xn, DeferredNorm):
             proj = self.qkv.forward_auto(xn.x, T)
@@ -150,6 +185,40 @@ class Attention(Mixer):
                 view.block_table, view.k, view.v, write_kv=writes,
                 cos_sin=self.position.cos_sin(batch))
             self.attend(q, attn, batch, view, window)
+        if sink is not None:
+            deferred = self.o.forward_residual(attn, T, sink)
+            if deferred is not None:
+                return deferred
+        if add_into is not None and self.o.forward_add(attn, T, add_into):
+            return None
+        return self.o.forward_delta(attn, T)
+
+    def _forward_padded(self, xn, batch, view, window, writes, sink, add_into):
+        """Heads of unequal sizes, neighbouring rotation pairs or a gate per head: one kernel rotates and pads
+        queries and keys, writes keys and values (padded) to their pages and takes the sigmoid of the gate
+        columns; the attention runs at the padded head size; one kernel multiplies each head by its gate and
+        drops the padding."""
+        T = batch.n_tokens
+        dev, act = self.env.device, self.env.act_dtype
+        if isinstance(xn, DeferredNorm):
+            xn = xn.materialize()
+        proj = self.qkv.forward_auto(xn, T)
+        q = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
+        gates = torch.empty((T, self.nq), dtype=torch.float32, device=dev) if self.gated else None
+        with scope(op="rotate_cache"):
+            kernels.qk_norm_rope_cache(
+                proj, q, T, self.nq, self.nkv, self.hd, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+                self.position.inv_freq, self.position.rot_dim, batch.positions, batch.slot_of_token,
+                view.block_table, view.k, view.v, write_kv=writes, cos_sin=self.position.cos_sin(batch),
+                v_head_dim=self.vd, padded_head_dim=self.hdp, interleaved=getattr(self.position, "interleaved", False),
+                gates=gates)
+        attn = torch.empty((T, self.nq * self.hdp), dtype=act, device=dev)
+        paged_attention(q, attn, batch, view.k, view.v, view.block_table, self.nq, self.nkv, self.hdp, self.scale, window)
+        if self.gated or self.hdp != self.vd:
+            narrow = torch.empty((T, self.nq * self.vd), dtype=act, device=dev)
+            with scope(op="head_gate"):
+                kernels.head_gate(attn, narrow, gates, self.nq, self.hdp, self.vd, T)
+            attn = narrow
         if sink is not None:
             deferred = self.o.forward_residual(attn, T, sink)
             if deferred is not None:

@@ -9,7 +9,7 @@ import torch
 from ..config.specs import LayerSpec
 from ..profile import scope
 from ..weights.decl import TensorDecl
-from .base import (BuildEnv, NormedRows, ResidualSink, RoutedRows, build_feed_forward, build_mixer, build_norm,
+from .base import (BuildEnv, DeferredNorm, NormedRows, ResidualSink, RoutedRows, build_feed_forward, build_mixer, build_norm,
                    register_arrangement)
 
 
@@ -216,3 +216,74 @@ class SandwichNormBlock:
         if norm is None:
             return None
         return NormedRows(rows, None, norm.eps, self.hidden, norm, resid)
+
+
+@register_arrangement("parallel")
+class ParallelBlock:
+    """h = norm(x); x += mixer(h) + ff(h): one norm, and both sublayers read its output.
+
+    Both results travel as deltas (partial sums over K); the mixer's joins the 32-bit residual stream in a
+    small kernel of its own, the feed-forward's rides on to the next layer's norm (or the model's last one),
+    which adds it in the kernel that normalises.  For prompts the sublayers are offered to add into the residual
+    inside their last product instead.  A layer without a feed-forward has only the mixer."""
+
+    chains = False
+
+    def __init__(self, spec: LayerSpec, hidden: int, env: BuildEnv, mixer_spec=None):
+        self.spec = spec
+        self.prefix = spec.prefix
+        self.norm = build_norm(spec.mixer_norm, hidden, env)
+        self.mixer = build_mixer(mixer_spec or spec.mixer, hidden, env)
+        self.ff = build_feed_forward(spec.feed_forward, hidden, env) if spec.feed_forward is not None else None
+        self.mixer_norm = self.norm        # the name other arrangements look for in the block after them
+
+    def _parts(self):
+        p, s = self.prefix, self.spec
+        out = [(self.norm, f"{p}.{s.mixer_norm_name}"), (self.mixer, f"{p}.{s.mixer_name}")]
+        if self.ff is not None:
+            out.append((self.ff, f"{p}.{s.ff_name}"))
+        return out
+
+    def declare(self) -> List[TensorDecl]:
+        return [d for part, name in self._parts() for d in part.declare(name)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for part, name in self._parts():
+            part.load(tensors, name)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part, _ in self._parts())
+
+    def weight_bytes(self) -> int:
+        return sum(part.weight_bytes() for part, _ in self._parts())
+
+    def workspace_bytes(self, n_tokens: int) -> int:
+        """The norm's rows live through both sublayers, and the mixer's delta until the feed-forward is done."""
+        return self.norm.workspace_bytes(n_tokens) + self.mixer.workspace_bytes(n_tokens) + \
+            (self.ff.workspace_bytes(n_tokens) if self.ff is not None else 0)
+
+    def cost(self, q_lens, kv_lens):
+        parts = [part.cost(q_lens, kv_lens) for part, _ in self._parts()]
+        return sum(p[0] for p in parts), sum(p[1] for p in parts)
+
+    def forward(self, resid, pending, batch, view):
+        from .. import kernels
+        T = batch.n_tokens
+        adds = not batch.is_decode and T > ADD_INTO_MIN_TOKENS and _defer_enabled()
+        with scope(op="mixer_norm"):
+            xn = self.norm.forward(resid, pending, T)        # adds what the layer before left, then normalises
+        if isinstance(xn, DeferredNorm):
+            xn = xn.materialize()
+        if adds and getattr(self.mixer, "can_add_into", False):
+            delta = self.mixer.forward(xn, batch, view, add_into=resid)
+        else:
+            delta = self.mixer.forward(xn, batch, view)
+        if self.ff is None:
+            return delta
+        if delta is not None:
+            with scope(op="mixer_add"):
+                kernels.residual_inject(resid, delta)
+        if adds and getattr(self.ff, "can_add_into", False):
+            return self.ff.forward(xn, batch, add_into=resid)
+        return self.ff.forward(xn, batch)

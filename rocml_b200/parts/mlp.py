@@ -19,9 +19,11 @@ TENSOR_NAMES = {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
-    """gate and up are one stacked product [T, 2I]; SiLU(gate) * up -> [T, I]; down -> [T, H].
-    The activation is a parameter; 'silu' (g / (1 + exp(-g)), rocml-kernels/kernels/
-    silu_mul.hip:15-18) is the one built."""
+    """gate and up are one stacked product [T, 2I]; act(gate) * up -> [T, I]; down -> [T, H].
+    The activation is a parameter: 'silu' (g / (1 + exp(-g)), rocml-kernels/kernels/
+    silu_mul.hip:15-18), which the products apply in their epilogues, or 'gelu_tanh'
+    (g / 2 * (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))), applied by a kernel of its own on the
+    product's result (32-bit partial sums for few tokens)."""
 
     graph_safe = True
 
@@ -30,9 +32,9 @@ class GatedMLP(FeedForward):
         self.env = env
         self.hidden = hidden
         self.inter = int(p["intermediate"])
-        act = p.get("activation", "silu")
-        if act != "silu":
-            raise ConfigError(f"activation {act!r} is not built (only 'silu')")
+        self.act = act = p.get("activation", "silu")
+        if act not in ("silu", "gelu_tanh"):
+            raise ConfigError(f"activation {act!r} is not built (known: silu, gelu_tanh)")
         bias = bool(p.get("bias", False))
         try:
             n = tensor_names(p, TENSOR_NAMES)
@@ -47,7 +49,7 @@ class GatedMLP(FeedForward):
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         self.gate_up.load(tensors, prefix)
         self.down.load(tensors, prefix)
-        if self.env.act_dtype == torch.bfloat16:
+        if self.env.act_dtype == torch.bfloat16 and self.act == "silu":
             self.gate_up.interleave_pairs()     # silu(gate) * up then happens inside the product
 
     def weight_bytes(self) -> int:
@@ -93,7 +95,10 @@ class GatedMLP(FeedForward):
             # the product is split over K some other way, so the activation waits for the partial sums
             gu = self.gate_up.forward_auto(xn, T)      # [T, 2I] or [S, T, 2I] partial sums
             h = torch.empty((T, self.inter), dtype=act, device=dev)
-            kernels.silu_mul(gu, h, paired=self.gate_up.paired)
+            if self.act == "silu":
+                kernels.silu_mul(gu, h, paired=self.gate_up.paired)
+            else:
+                kernels.gated_act(gu, h, self.act, paired=self.gate_up.paired)
         if sink is not None:
             deferred = self.down.forward_residual(h, T, sink)
             if deferred is not None:

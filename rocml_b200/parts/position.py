@@ -3,6 +3,8 @@ pos * inv_freq[i]; the encoding owns that table, so another encoding (a partial 
 another base, scaled frequencies) is another table, not another kernel."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..config.specs import PositionSpec
@@ -22,14 +24,33 @@ class NoPosition(PositionEncoding):
         return None
 
 
+def stretch_long_waves(inv: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """Frequencies with the long wavelengths stretched, piecewise by wavelength L = 2 pi / f: unchanged where
+    L < original / high; f / factor where L > original / low; between the two a blend,
+    s = (original / L - low) / (high - low), (1 - s) f / factor + s f.  Double precision in and out."""
+    if not (factor > 0 and high > low >= 0 and original > 0):
+        raise ConfigError(f"frequency scaling needs factor > 0, high > low >= 0 and original > 0 "
+                          f"(found factor {factor}, low {low}, high {high}, original {original})")
+    wave = 2.0 * math.pi / inv
+    s = (original / wave - low) / (high - low)
+    blend = (1.0 - s) * inv / factor + s * inv
+    out = torch.where(wave < original / high, inv, blend)
+    if low > 0:
+        out = torch.where(wave > original / low, inv / factor, out)
+    return out
+
+
 @register_position("rope_neox")
 class RotaryNeox(PositionEncoding):
     """Rotate-half rotary embedding: inv_freq[i] = theta^(-2i / rot_dim) for i < rot_dim / 2,
     pairs (i, i + rot_dim / 2) (rocml-kernels/kernels/rope.hip:18-33).  The exponent and the
     power are evaluated in double precision and rounded once to float32; the angle
-    pos * inv_freq and its sine and cosine are 32-bit, in the kernel."""
+    pos * inv_freq and its sine and cosine are 32-bit, in the kernel.  Parameter ``scaling``
+    ({factor, low, high, original}) stretches the long wavelengths (``stretch_long_waves``)."""
 
     graph_safe = True
+    interleaved = False        # which entries of a head form a pair: (i, i + rot_dim / 2)
+    kind = "rope_neox"
 
     def __init__(self, spec: PositionSpec, head_dim: int, env: BuildEnv):
         rot = head_dim if spec.rot_dim is None else int(spec.rot_dim)
@@ -41,16 +62,31 @@ class RotaryNeox(PositionEncoding):
         self.theta = float(spec.theta)
         i = torch.arange(rot // 2, dtype=torch.float64)
         inv = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / rot)
+        sc = spec.params.get("scaling")
+        self.scaling = None
+        if sc:
+            sc = dict(sc)
+            self.scaling = tuple(float(sc[k]) for k in ("factor", "low", "high", "original"))
+            inv = stretch_long_waves(inv, *self.scaling)
         self.inv_freq = inv.to(torch.float32).to(env.device)
 
     def cos_sin(self, batch):
         """(cos, sin) of every token's angles for this step, computed once and shared by all the
         layers that use this encoding with the same table."""
         from .. import kernels
-        key = ("rope_neox", self.rot_dim, self.theta)      # layers with the same encoding share the table
+        key = ("rope", self.rot_dim, self.theta, self.scaling)      # layers with the same angles share the table
         if key not in batch.scratch:
             batch.scratch[key] = kernels.rope_table(batch.positions, self.inv_freq, batch.n_tokens)
         return batch.scratch[key]
+
+
+@register_position("rope_pairs")
+class RotaryPairs(RotaryNeox):
+    """The same rotation with neighbouring entries as pairs: (2i, 2i + 1) turn by pos * inv_freq[i],
+    i < rot_dim / 2; the entries from rot_dim on pass unchanged.  Same table, same parameters."""
+
+    interleaved = True
+    kind = "rope_pairs"
 
 
 @register_position("sinusoid")

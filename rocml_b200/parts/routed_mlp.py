@@ -6,7 +6,12 @@
 
 ``activation`` "silu": silu(g) * u.  "clamped_swish": g = min(g, limit), u = clamp(u, -limit, limit),
 g * sigmoid(alpha * g) * (u + 1).  ``choice_bias`` adds a per-expert vector to the scores for the choice
-only; the weights are the scores themselves, renormalised over the chosen if ``renormalize`` says so.
+only; the weights are the scores themselves, divided by their sum over the chosen (+ ``renormalize_eps``) if
+``renormalize`` says so.  ``groups`` > 1: the experts form that many equal groups of neighbours, a group's
+score is the sum of its two largest scores, and only experts of the ``keep_groups`` best groups can be chosen.
+``shared`` (an intermediate size): one more expert of the same form that every token uses, its result multiplied
+by sigmoid(w_sg . h) (one number a token) when ``shared_gate`` says so; the gate's row rides along with the
+router's rows in the 32-bit router product, and the shared result joins in the kernel that sums the choices.
 
 How a step runs, without the host ever learning who chose what (so a decode step is one CUDA graph):
 the router's product, one kernel that scores, chooses and counts, one that lays every expert's rows out
@@ -31,7 +36,7 @@ from ..weights.decl import TensorDecl
 from .base import BuildEnv, FeedForward, RoutedRows, register_feed_forward
 
 TENSOR_NAMES = {"router": "gate", "choice_bias": "e_score_correction_bias", "expert": "experts.{e}.", "gate": "gate_proj",
-                "up": "up_proj", "down": "down_proj"}
+                "up": "up_proj", "down": "down_proj", "shared": "shared_experts.", "shared_gate": "shared_expert_gate"}
 
 SMALL_TILE, LARGE_TILE, TENSOR_TILE = 16, 64, 128
 SMALL_TILE_MAX_ROWS = 256      # token-choices up to which the 16-row tile is used
@@ -61,9 +66,27 @@ class RoutedMLP(FeedForward):
             raise ConfigError("routed_mlp: clamped_swish needs a positive limit")
         if p.get("score", "sigmoid") != "sigmoid":
             raise ConfigError(f"routed_mlp: score {p.get('score')!r} is not built (only 'sigmoid')")
-        if p.get("renormalize", False):
-            raise ConfigError("routed_mlp: renormalised weights are not built")
+        self.renormalize = bool(p.get("renormalize", False))
+        self.renormalize_eps = float(p.get("renormalize_eps", 0.0))
+        self.groups = int(p.get("groups") or 1)
+        self.keep_groups = int(p.get("keep_groups") or self.groups)
+        if self.groups < 1 or self.experts % self.groups or not 1 <= self.keep_groups <= self.groups or \
+                self.keep_groups * (self.experts // self.groups) < self.top:
+            raise ConfigError(f"routed_mlp: {self.groups} groups of which {self.keep_groups} stay do not fit "
+                              f"{self.experts} experts with {self.top} chosen")
         self.has_bias = bool(p.get("choice_bias", False))
+        self.shared_inter = int(p.get("shared") or 0)
+        self.shared_gated = bool(p.get("shared_gate", False)) and self.shared_inter > 0
+        self.shared = None
+        if self.shared_inter:
+            if self.act != "silu":
+                raise ConfigError("routed_mlp: the shared expert is built with the 'silu' activation only")
+            from ..config.specs import FeedForwardSpec
+            from .mlp import GatedMLP
+            names = dict(p.get("names") or ())
+            self.shared = GatedMLP(FeedForwardSpec.make(
+                "gated_mlp", intermediate=self.shared_inter, activation="silu", bias=False,
+                names={r: names[r] for r in ("gate", "up", "down") if r in names}), hidden, env)
         try:
             self.names = tensor_names(p, TENSOR_NAMES)
         except ValueError as e:
@@ -81,6 +104,10 @@ class RoutedMLP(FeedForward):
         out = [TensorDecl(f"{prefix}{self.names['router']}.weight", (self.experts, self.hidden), "matrix")]
         if self.has_bias:
             out.append(TensorDecl(f"{prefix}{self.names['choice_bias']}.weight", (self.experts,), "bias"))
+        if self.shared is not None:
+            out += self.shared.declare(prefix + self.names["shared"])
+        if self.shared_gated:
+            out.append(TensorDecl(f"{prefix}{self.names['shared']}{self.names['shared_gate']}.weight", (1, self.hidden), "matrix"))
         for e in range(self.experts):
             out += [TensorDecl(self._expert(prefix, e, "gate"), (self.inter, self.hidden), "matrix"),
                     TensorDecl(self._expert(prefix, e, "up"), (self.inter, self.hidden), "matrix"),
@@ -89,6 +116,12 @@ class RoutedMLP(FeedForward):
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         self.router = tensors[f"{prefix}{self.names['router']}.weight"].float().contiguous()     # the router is 32-bit
+        if self.shared is not None:
+            self.shared.load(tensors, prefix + self.names["shared"])
+        if self.shared_gated:
+            # the shared expert's gate is one more row of the router's product
+            sg = tensors[f"{prefix}{self.names['shared']}{self.names['shared_gate']}.weight"].float().reshape(1, self.hidden)
+            self.router = torch.cat([self.router, sg], dim=0).contiguous()
         if self.has_bias:
             self.choice_bias = tensors[f"{prefix}{self.names['choice_bias']}.weight"].float().contiguous()
         gu = [torch.cat([tensors[self._expert(prefix, e, "gate")], tensors[self._expert(prefix, e, "up")]], dim=0)
@@ -104,7 +137,8 @@ class RoutedMLP(FeedForward):
     def weight_bytes(self) -> int:
         """What a step reads at most: the router and the experts that can be chosen."""
         esz = 4 if self.env.mode == "float32" else 2
-        return self.experts * self.hidden * 4 + self.experts * 3 * self.inter * self.hidden * esz
+        shared = self.shared.weight_bytes() if self.shared is not None else 0
+        return self.experts * self.hidden * 4 + self.experts * 3 * self.inter * self.hidden * esz + shared
 
     def _expected_experts(self, n_tokens: int) -> float:
         """The experts ``n_tokens`` tokens touch when each picks ``top`` of them at random."""
@@ -129,7 +163,8 @@ class RoutedMLP(FeedForward):
     def workspace_bytes(self, n_tokens: int) -> int:
         esz = 4 if self.env.mode == "float32" else 2
         rows = self._max_tiles(n_tokens) * self._tile(n_tokens)
-        return rows * (self.hidden * (esz + 4) + self.inter * 3 * esz) + n_tokens * (self.hidden * 4 + self.experts * 4)
+        shared = self.shared.workspace_bytes(n_tokens) if self.shared is not None else 0
+        return rows * (self.hidden * (esz + 4) + self.inter * 3 * esz) + n_tokens * (self.hidden * 4 + self.experts * 4) + shared
 
     def cost(self, q_lens, kv_lens):
         T = sum(q_lens)
@@ -138,7 +173,11 @@ class RoutedMLP(FeedForward):
         # picks ``top`` of them at random (all of them for a prompt, a part of them for a few tokens)
         used = self._expected_experts(T)
         nbytes = self.experts * self.hidden * 4 + int(used * 3 * self.inter * self.hidden * esz)
-        return nbytes, 2 * T * self.experts * self.hidden + 2 * T * self.top * 3 * self.inter * self.hidden
+        flops = 2 * T * self.experts * self.hidden + 2 * T * self.top * 3 * self.inter * self.hidden
+        if self.shared is not None:
+            sb, sf = self.shared.cost(q_lens, kv_lens)
+            nbytes, flops = nbytes + sb, flops + sf
+        return nbytes, flops
 
     sums_later = True      # forward() accepts sum_later=True and may then return RoutedRows (see parts.base)
 
@@ -149,7 +188,7 @@ class RoutedMLP(FeedForward):
         tile = self._tile(T)
         max_tiles = self._max_tiles(T)
         rows = max_tiles * tile
-        z = torch.empty((T, E), dtype=torch.float32, device=dev)
+        z = torch.empty((T, self.router.shape[0]), dtype=torch.float32, device=dev)    # E scores (+ the shared expert's gate)
         with scope(op="router"):
             kernels.router_logits(xn, self.router, z, T)
         ids = torch.empty((T, top), dtype=torch.int32, device=dev)
@@ -160,7 +199,9 @@ class RoutedMLP(FeedForward):
         tile_group = torch.empty((max_tiles,), dtype=torch.int32, device=dev)
         row_of = torch.empty((T, top), dtype=torch.int32, device=dev)
         with scope(op="route"):
-            kernels.moe_route(z, self.choice_bias, batch.slot_of_token, T, top, ids, weights, place, counts)
+            kernels.moe_route(z, self.choice_bias, batch.slot_of_token, T, top, ids, weights, place, counts,
+                              n_groups=self.groups, keep_groups=self.keep_groups, renormalize=self.renormalize,
+                              norm_eps=self.renormalize_eps)
             kernels.moe_plan(counts, tile, starts, tile_group)
             xs = torch.empty((rows, self.hidden), dtype=act, device=dev)
             kernels.moe_gather(xn, ids, place, starts, T, top, xs, row_of)
@@ -185,6 +226,15 @@ class RoutedMLP(FeedForward):
             if not (tile == TENSOR_TILE and kernels.tile_matmul_tc5(y, self.down, out_rows, tile_group, **told)):
                 kernels.tile_matmul(y, self.down, out_rows, tile_group, tile, **told)
         routed = RoutedRows(out_rows, row_of, weights, top, T)
+        if self.shared is not None:
+            # the expert every token uses: its partial sums join where the choices are summed
+            with scope(op="shared_expert"):
+                extra = self.shared.forward(xn, batch)
+            out = torch.empty((1, T, self.hidden), dtype=torch.float32, device=dev)
+            with scope(op="experts_sum"):
+                kernels.moe_combine(out_rows, row_of, weights, T, top, out[0], extra=extra,
+                                    extra_gate=z[:, E] if self.shared_gated else None)
+            return out
         if sum_later:
             return routed
         with scope(op="experts_sum"):

@@ -50,6 +50,13 @@ def qk_norm_rope(rows: int, nq: int, nkv: int, hd: int, n_in: int, in_esz: int, 
     return rows * (width * in_esz * n_in + out * out_esz), rows * (nq + nkv) * hd * 10
 
 
+def decay_scan(tokens: int, seqs: int, heads: int, dim: int, vdim: int, n_in: int, in_esz: int) -> Cost:
+    """A decayed running sum per (sequence, head): the tokens' q, k, v in, every sequence's 32-bit state in and
+    back, 32-bit results out; per token and state entry a decay, an update and a product with q."""
+    nbytes = tokens * heads * (2 * dim + vdim) * in_esz * n_in + 2 * seqs * heads * dim * vdim * 4 + tokens * heads * vdim * 4
+    return nbytes, 5 * tokens * heads * dim * vdim
+
+
 def rope_table(rows: int, half: int) -> Cost:
     return rows * (4 + half * 8) + half * 4, rows * half * 40
 
@@ -59,12 +66,25 @@ def attention(q_lens: Iterable[int], kv_lens: Iterable[int], nq: int, nkv: int, 
     """Softmax attention of each sequence's last ``q_len`` positions over its own keys: the keys and
     values a sequence's queries can see once (grouped heads share them: the traffic scales with the
     key/value heads, rocml/src/profile/cost.rs:58-68), queries in, outputs out; 4 operations per
-    (query head, visible key, head dimension) (rocml/src/profile/cost.rs:75-77)."""
+    (query head, visible key, head dimension) (rocml/src/profile/cost.rs:75-77).  ``window`` n > 0: the last
+    n keys; -n: the keys of the query's own block of n positions."""
     nbytes = flops = 0
     for ql, kl in zip(q_lens, kv_lens):
         if ql <= 0 or kl <= 0:
             continue
         first = kl - ql                                          # position of the first query
+        if window and window < 0:
+            size = -window
+            seen_from = first - first % size
+            nbytes += 2 * nkv * (kl - seen_from) * hd * esz + 2 * ql * nq * hd * esz
+            pairs, p = 0, first
+            while p < kl:                                        # a query at offset r of its block sees r + 1 keys
+                end = min(kl, p - p % size + size)
+                a, b = p % size + 1, (end - 1) % size + 1
+                pairs += (a + b) * (b - a + 1) // 2
+                p = end
+            flops += 4 * nq * hd * pairs
+            continue
         seen_from = max(0, first - window + 1) if window else 0  # the oldest key any query sees
         nbytes += 2 * nkv * (kl - seen_from) * hd * esz + 2 * ql * nq * hd * esz
         if window:
