@@ -67,7 +67,8 @@ def attention(q, k, v, window=None, scale=None):
     attention.rs:160); the query at position p sees j in [0, p] (attn_prefill.hip:57-60,121);
     softmax with the maximum subtracted (attn_decode.hip:160-170); o = sum p_j v_j / l
     (attn_prefill.hip:201-203).  ``window`` n keeps only j > p - n (the reference has no
-    window; this is the sliding_window key of Qwen3's config.json).
+    window; this is the sliding_window key of Qwen3's config.json); a negative ``window`` -n
+    keeps only the keys of the query's own block of n positions, j // n == p // n.
     q: [T, nq, hd]; k, v: [T, nkv, hd]; returns [T, nq, hd].
     """
     T, nq, hd = q.shape
@@ -77,8 +78,10 @@ def attention(q, k, v, window=None, scale=None):
     out = torch.empty_like(q)
     pos = torch.arange(T)
     allowed = pos[None, :] <= pos[:, None]
-    if window is not None:
+    if window is not None and window > 0:
         allowed &= pos[None, :] > pos[:, None] - window
+    elif window is not None and window < 0:
+        allowed &= (pos[None, :] // -window) == (pos[:, None] // -window)
     for h in range(nq):
         kh, vh = k[:, h // g, :], v[:, h // g, :]
         s = (q[:, h, :] @ kh.t()) * scale

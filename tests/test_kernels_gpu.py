@@ -430,6 +430,9 @@ ATT_CASES = [
     ([300, 131], [300, 3], 5, 5, 48, 24),                # a window, no grouping, head size 48
     ([700], [1], 32, 8, 128, None),                      # one far key among hundreds
     ([260, 90], [65, 90], 20, 1, 64, 100),               # a group wider than a block's 16 rows
+    ([300, 131, 64], [300, 3, 1], 6, 2, 48, -37),        # blocks of 37 positions instead of a window
+    ([200, 129], [72, 129], 4, 4, 32, -64),              # blocks of exactly a page; a piece that starts inside a block
+    ([90], [90], 3, 1, 16, -1),                          # blocks of one position: every query sees itself only
 ]
 
 
@@ -459,6 +462,8 @@ PRE_CASES = [
     ([300, 131], [300, 3], 4, 4, 128, 24),                     # a window narrower than a tile
     ([900], [333], 6, 1, 64, 200),                             # a window that spans tiles; 6:1 groups
     ([513], [513], 2, 1, 256, None),
+    ([700, 130], [700, 100], 4, 2, 64, -150),                  # blocks of 150 positions: rows of one tile in two blocks
+    ([333], [120], 2, 2, 128, -50),                            # blocks narrower than a tile, a piece of a prompt
 ]
 
 
@@ -494,6 +499,9 @@ TC5_CASES = [
     PRE_CASES[3],                                                  # head size 64, a window, 6:1 groups
     PRE_CASES[4],                                                  # head size 256
     ([700, 130], [450, 130], 4, 2, 256, 150),                      # head size 256: a piece of a prompt, a window
+    ([900, 64], [900, 64], 4, 2, 128, -200),                       # blocks of 200 positions
+    ([520, 257], [300, 130], 6, 1, 64, -33),                       # blocks narrower than a tile; pieces of prompts
+    ([400], [400], 2, 2, 128, -128),                               # blocks of exactly two pages
 ]
 
 
@@ -558,6 +566,9 @@ DEC_CASES = [
     ([513, 40], 6, 3, 128, 70),
     ([1000], 2, 2, 256, None),
     ([257, 100, 31], 12, 2, 64, 33),
+    ([513, 200, 201, 64, 65], 8, 2, 64, -200),      # blocks of 200 positions: the last, the first and a middle place of a block
+    ([300, 129], 4, 4, 128, -64),                   # blocks of exactly a page
+    ([77, 5], 6, 3, 64, -1),                        # blocks of one position
 ]
 
 

@@ -148,3 +148,103 @@ def write_pipilix(folder, cfg_dict, seed, std=0.05, sharp=1.0, bias_std=0.5, rou
             w[k] = (w[k].float() * (bias_std / 0.02)).to(torch.bfloat16)
     save_file(w, path)
     return folder
+
+
+# ---- Zokelorn: small configurations that differ in every size, option and constant --------------------------------
+def _zattn(heads, kv, dim, vdim, block, scale, rot_dims, base=10000.0, scaling=None):
+    rot = {"base": base, "dims": rot_dims}
+    if scaling is not None:
+        rot["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale,
+                                          "mask": {"size": block}, "rot": rot}}
+
+
+def _zdecay(kind, heads, dim, vdim, decay):
+    return {"type": kind, "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}}
+
+
+def _zmoe(ff, experts, top, groups=None, shared=None):
+    router = {"experts": experts, "top": top}
+    if groups is not None:
+        router["groups"] = {"count": groups[0], "keep": groups[1]}
+    d = {"kind": "moe", "expert": {"ff": ff}, "router": router}
+    if shared is not None:
+        d["shared"] = {"ff": shared}
+    return d
+
+
+def _z(layer, mlp):
+    return {**layer, "mlp": mlp}
+
+
+# ZA: a loop from the first layer that runs three times; value heads wider and narrower than key heads; a rotation of
+# half of every head with stretched long waves; blocks of 37 positions; groups of experts; a layer without feed-forward
+ZOKELORN_A = {
+    "architecture": "Zokelorn", "vocab": 211, "width": 64, "norm": {"eps": 1e-6}, "loop": {"start": 0, "stop": 2, "times": 3},
+    "layers": [_z(_zdecay("lightning", 3, 16, 24, (0.5, 0.9, 0.99)), _dense(96)),
+               _z(_zattn(4, 2, 32, 16, 37, 0.3, 16, 10000.0, (4.0, 1.0, 2.0, 64)), _zmoe(24, 6, 2, (3, 2), 40)),
+               _z(_zdecay("retention", 2, 24, 8, (0.97, 0.75)), None)],
+}
+# ZB: no loop; head sizes 64 and 128 (which the bfloat16 attention kernels take), one key/value head for eight query
+# heads, blocks of exactly one page, one expert a token of sixteen without groups or a shared expert
+ZOKELORN_B = {
+    "architecture": "Zokelorn", "vocab": 333, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [_z(_zattn(8, 1, 64, 64, 64, 0.125, 64, 1000000.0), _zmoe(64, 16, 1)),
+               _z(_zdecay("lightning", 4, 64, 64, (0.999, 0.9, 0.8, 0.95)), _dense(160)),
+               _z(_zdecay("retention", 5, 8, 40, (0.9, 0.99, 0.999, 0.5, 0.7)), _zmoe(48, 4, 3, None, 32)),
+               _z(_zattn(2, 2, 128, 128, 300, 0.09, 32, 500.0, (8.0, 1.0, 4.0, 256)), _dense(96))],
+}
+# ZC: sizes that are multiples of four only, head sizes that are no multiple of 16, every expert chosen, every group
+# kept, blocks of one position, a loop that runs once, decays of 0 and 1
+ZOKELORN_C = {
+    "architecture": "Zokelorn", "vocab": 97, "width": 72, "norm": {"eps": 3e-5}, "loop": {"start": 1, "stop": 2, "times": 1},
+    "layers": [_z(_zattn(3, 3, 20, 28, 1, 0.5, 12, 100.0), _zmoe(28, 4, 4, (2, 2), 16)),
+               _z(_zdecay("retention", 1, 40, 12, (1.0,)), _dense(52)),
+               _z(_zdecay("lightning", 7, 4, 4, (0.0, 0.3, 0.6, 0.9, 0.95, 0.99, 1.0)), _zmoe(20, 9, 2, (3, 1)))],
+}
+# ZD: a width that is a multiple of four only, more query heads a key/value head than one block of the decode kernel
+# takes, a single expert, key heads of 128 with value heads of 64, no rotation at all, a block that ends inside the
+# second page
+ZOKELORN_D = {
+    "architecture": "Zokelorn", "vocab": 150, "width": 100, "norm": {"eps": 1e-6}, "loop": {"start": 1, "stop": 3, "times": 2},
+    "layers": [_z(_zattn(20, 1, 16, 16, 90, 0.4, 0), _zmoe(32, 1, 1, None, 24)),
+               _z(_zattn(6, 2, 128, 64, 130, 0.2, 128, 30000.0, (2.0, 0.5, 3.0, 32)), _dense(64)),
+               _z(_zdecay("lightning", 2, 72, 136, (0.98, 0.6)), _zmoe(12, 8, 3, (4, 2), 20))],
+}
+ZOKELORN = {"ZA": ZOKELORN_A, "ZB": ZOKELORN_B, "ZC": ZOKELORN_C, "ZD": ZOKELORN_D}
+
+
+def write_zokelorn(folder, cfg_dict, seed, std=0.05, sharp=1.0, router_gain=3.0, fixed_routes=False):
+    """A Zokelorn model folder with random weights.  ``std``: the matrices' standard deviation; ``sharp`` multiplies
+    the attention layers' query matrices, so that the softmax picks few keys and a key wrongly seen or missed
+    moves the result; ``router_gain`` multiplies the routers, which spreads the scores (fewer near ties).
+    ``fixed_routes``: every token makes the same choices, by a wide margin: entry 0 of the stream is the same
+    large number for every token and stays so (no layer writes to it), and a router's row for expert e is
+    c_e times the unit vector 0, the c_e far enough apart that no rounding changes an order."""
+    from safetensors.torch import load_file, save_file
+    write_model(folder, cfg_dict, seed)
+    path = os.path.join(folder, "model.safetensors")
+    w = load_file(path)
+    g = torch.Generator().manual_seed(seed)
+    for k in sorted(w):
+        if w[k].dim() != 2:
+            continue
+        f = std / 0.02
+        if k.endswith(".mix.q") and cfg_dict["layers"][int(k.split(".")[0][1:])]["type"] == "attention":
+            f *= sharp
+        if k.endswith(".mlp.router"):
+            f *= router_gain
+        t = w[k].float() * f
+        if fixed_routes:
+            if k == "embed":
+                t[:, 0] = 4.0 * std         # a few times the other entries: the norm's output there is about 3
+            elif k.endswith(".o") or k.endswith(".down"):
+                t[0, :] = 0.0
+            elif k.endswith(".mlp.router"):
+                E = t.shape[0]
+                order = torch.randperm(E, generator=g).float()
+                t = torch.zeros_like(t)
+                t[:, 0] = (order - (E - 1) / 2.0) * min(0.25, 2.0 / E)
+        w[k] = t.to(torch.bfloat16)
+    save_file(w, path)
+    return folder
