@@ -113,6 +113,226 @@ decay_scan_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row
     }
 }
 
+// ---- prompts: the same sums by blocks of 64 tokens, all blocks at once ----------------------------------------------
+// Within a block of m tokens that starts from the state S0:
+//   o_t   = d^(t+1) S0^T q_t + sum_{s <= t} d^(t-s) (q_t . k_s) v_s           t = 0 .. m-1
+//   S_end = d^m S0 + sum_s d^(m-1-s) k_s v_s^T
+// Three kernels: (1) every block's own sum L = sum_s d^(m-1-s) k_s v_s^T; (2) along each sequence, S0 of every block
+// from the slot's state and the L's before it (the L's place receives S0; the slot receives the last S_end);
+// (3) every block's outputs.  A block of the grid finds its (sequence, block of tokens) from cu_q.  All 32-bit FMA.
+constexpr int CB = 64;              // tokens a block
+constexpr int CT = 256;             // threads
+
+__device__ __forceinline__ float decay_pow(float d, int n) {
+    float r = 1.f, b = d;
+    while (n > 0) { if (n & 1) r *= b; b *= b; n >>= 1; }
+    return r;
+}
+
+// Which sequence and which of its blocks of tokens the grid's block `g` is: blocks are numbered sequence after
+// sequence.  Returns false when g lies past the last one.  t0, m: the block's first row and its rows; first: the number
+// of the sequence's first block; slot: the sequence's slot (-1: padding).
+__device__ __forceinline__ bool find_block(int g, const int* seq_slot, const int* cu_q, int B, int* b_out, int* t0, int* m,
+                                           int* first, int* slot) {
+    int base = 0;
+    for (int b = 0; b < B; ++b) {
+        const int n = cu_q[b + 1] - cu_q[b];
+        const int nb = seq_slot[b] >= 0 ? (n + CB - 1) / CB : 0;
+        if (g < base + nb) {
+            const int c = g - base;
+            *b_out = b; *t0 = cu_q[b] + c * CB; *m = min(CB, n - c * CB); *first = base; *slot = seq_slot[b];
+            return true;
+        }
+        base += nb;
+    }
+    return false;
+}
+
+template <typename IT>
+__device__ __forceinline__ void stage_rows(const IT* in, int n_in, size_t in_stride, int row_stride, int t0, int m, int col0,
+                                           int width, int act, float* dst, int ld, const float* row_factor, float factor) {
+    for (int idx = threadIdx.x; idx < m * width; idx += CT) {
+        const int tt = idx / width, i = idx - tt * width;
+        float x = load_sum(in + (size_t)(t0 + tt) * row_stride + col0 + i, n_in, in_stride);
+        if (act == 1) x = silu(x);
+        dst[tt * ld + i] = x * factor * (row_factor ? row_factor[tt] : 1.f);
+    }
+}
+
+template <typename IT, int R>
+__global__ void __launch_bounds__(CT)
+chunk_state_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int k_off, int v_off, int heads,
+                   int dim, int vdim, int act_qk, int act_v, float k_scale, const float* __restrict__ decay,
+                   const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int B, float* __restrict__ Lbuf) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float pw[CB + 1];
+    int b, t0, m, first, slot;
+    if (!find_block(blockIdx.x, seq_slot, cu_q, B, &b, &t0, &m, &first, &slot)) return;
+    const int h = blockIdx.y;
+    const float d = decay[h];
+    float* ks = sm;                       // [m][dim], row s already times d^(m-1-s)
+    float* vs = ks + CB * dim;            // [m][vdim]
+    if (threadIdx.x < m) pw[threadIdx.x] = decay_pow(d, m - 1 - threadIdx.x);
+    __syncthreads();
+    stage_rows(in, n_in, in_stride, row_stride, t0, m, k_off + h * dim, dim, act_qk, ks, dim, pw, k_scale);
+    stage_rows(in, n_in, in_stride, row_stride, t0, m, v_off + h * vdim, vdim, act_v, vs, vdim, nullptr, 1.f);
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[R][R];
+#pragma unroll
+    for (int a = 0; a < R; ++a)
+#pragma unroll
+        for (int c = 0; c < R; ++c) acc[a][c] = 0.f;
+    for (int s = 0; s < m; ++s) {
+        float kk[R], vv[R];
+#pragma unroll
+        for (int a = 0; a < R; ++a) kk[a] = ty + 16 * a < dim ? ks[s * dim + ty + 16 * a] : 0.f;
+#pragma unroll
+        for (int c = 0; c < R; ++c) vv[c] = tx + 16 * c < vdim ? vs[s * vdim + tx + 16 * c] : 0.f;
+#pragma unroll
+        for (int a = 0; a < R; ++a)
+#pragma unroll
+            for (int c = 0; c < R; ++c) acc[a][c] = fmaf(kk[a], vv[c], acc[a][c]);
+    }
+    float* L = Lbuf + ((size_t)blockIdx.x * heads + h) * dim * vdim;
+#pragma unroll
+    for (int a = 0; a < R; ++a)
+#pragma unroll
+        for (int c = 0; c < R; ++c)
+            if (ty + 16 * a < dim && tx + 16 * c < vdim) L[(size_t)(ty + 16 * a) * vdim + tx + 16 * c] = acc[a][c];
+}
+
+__global__ void __launch_bounds__(256)
+chunk_prefix_kernel(const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ seq_slot,
+                    const int* __restrict__ cu_q, int B, int heads, int dim, int vdim, float* __restrict__ Lbuf) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int n = cu_q[b + 1] - cu_q[b];
+    if (n <= 0) return;
+    int first = 0;
+    for (int i = 0; i < b; ++i)
+        if (seq_slot[i] >= 0) first += (cu_q[i + 1] - cu_q[i] + CB - 1) / CB;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= dim * vdim) return;
+    const float d = decay[h];
+    const float d_full = decay_pow(d, CB);
+    float* st = state + ((size_t)slot * heads + h) * dim * vdim + e;
+    float run = *st;
+    const int nb = (n + CB - 1) / CB;
+    for (int c = 0; c < nb; ++c) {
+        float* L = Lbuf + ((size_t)(first + c) * heads + h) * dim * vdim + e;
+        const float own = *L;
+        *L = run;                                             // the state this block of tokens starts from
+        const int m = min(CB, n - c * CB);
+        run = fmaf(m == CB ? d_full : decay_pow(d, m), run, own);
+    }
+    *st = run;
+}
+
+template <typename IT, int R>
+__global__ void __launch_bounds__(CT)
+chunk_out_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int q_off, int k_off, int v_off,
+                 int heads, int dim, int vdim, int act_qk, int act_v, float k_scale, const float* __restrict__ decay,
+                 const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int B, const float* __restrict__ Lbuf,
+                 float* __restrict__ out, int ld_out) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float pw[CB + 1];
+    int b, t0, m, first, slot;
+    if (!find_block(blockIdx.x, seq_slot, cu_q, B, &b, &t0, &m, &first, &slot)) return;
+    const int h = blockIdx.y;
+    const float d = decay[h];
+    const int ldq = dim + 1;
+    float* qs = sm;                        // [CB][dim + 1]
+    float* ks = qs + CB * ldq;             // [CB][dim + 1]; later slabs of the starting state
+    float* vs = ks + CB * ldq;             // [CB][vdim]
+    float* A = vs + CB * vdim;             // [CB][CB + 1]
+    if (threadIdx.x <= CB) pw[threadIdx.x] = decay_pow(d, threadIdx.x);
+    stage_rows(in, n_in, in_stride, row_stride, t0, m, q_off + h * dim, dim, act_qk, qs, ldq, nullptr, 1.f);
+    stage_rows(in, n_in, in_stride, row_stride, t0, m, k_off + h * dim, dim, act_qk, ks, ldq, nullptr, k_scale);
+    stage_rows(in, n_in, in_stride, row_stride, t0, m, v_off + h * vdim, vdim, act_v, vs, vdim, nullptr, 1.f);
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    {
+        // A[t][s] = d^(t-s) (q_t . k_s) for s <= t, else 0: t = ty + 16 a, s = tx + 16 c
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
+        for (int i = 0; i < dim; ++i) {
+            float qq[4], kk[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) qq[a] = ty + 16 * a < m ? qs[(ty + 16 * a) * ldq + i] : 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) kk[c] = tx + 16 * c < m ? ks[(tx + 16 * c) * ldq + i] : 0.f;
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[a][c] = fmaf(qq[a], kk[c], acc[a][c]);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int t = ty + 16 * a, s = tx + 16 * c;
+                A[t * (CB + 1) + s] = (s <= t && t < m) ? acc[a][c] * pw[t - s] : 0.f;
+            }
+    }
+    __syncthreads();
+    // o[t][j]: t = ty + 16 a (a < 4), j = tx + 16 c (c < R)
+    float o1[4][R], o2[4][R];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < R; ++c) { o1[a][c] = 0.f; o2[a][c] = 0.f; }
+    for (int s = 0; s < m; ++s) {
+        float aa[4], vv[R];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) aa[a] = A[(ty + 16 * a) * (CB + 1) + s];
+#pragma unroll
+        for (int c = 0; c < R; ++c) vv[c] = tx + 16 * c < vdim ? vs[s * vdim + tx + 16 * c] : 0.f;
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < R; ++c) o1[a][c] = fmaf(aa[a], vv[c], o1[a][c]);
+    }
+    // the part that comes from before the block: slabs of 32 rows of the starting state go through ks
+    const float* S0 = Lbuf + ((size_t)blockIdx.x * heads + h) * dim * vdim;
+    for (int i0 = 0; i0 < dim; i0 += 32) {
+        __syncthreads();
+        const int rows = min(32, dim - i0);
+        for (int idx = threadIdx.x; idx < rows * vdim; idx += CT) ks[idx] = S0[(size_t)i0 * vdim + idx];
+        __syncthreads();
+        for (int i = 0; i < rows; ++i) {
+            float qq[4], ss[R];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) qq[a] = ty + 16 * a < m ? qs[(ty + 16 * a) * ldq + i0 + i] : 0.f;
+#pragma unroll
+            for (int c = 0; c < R; ++c) ss[c] = tx + 16 * c < vdim ? ks[i * vdim + tx + 16 * c] : 0.f;
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int c = 0; c < R; ++c) o2[a][c] = fmaf(qq[a], ss[c], o2[a][c]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int t = ty + 16 * a;
+        if (t >= m) continue;
+        const float f = pw[t + 1];
+#pragma unroll
+        for (int c = 0; c < R; ++c)
+            if (tx + 16 * c < vdim) out[(size_t)(t0 + t) * ld_out + (size_t)h * vdim + tx + 16 * c] = fmaf(f, o2[a][c], o1[a][c]);
+    }
+}
+
 // One block a token.  in: o float32 [T, W]; gate: columns g_off .. g_off + W of the projection rows.
 template <typename IT, typename AT, typename WT>
 __global__ void __launch_bounds__(256)
@@ -225,6 +445,42 @@ extern "C" int rb_group_norm_gate(const float* o, int ld_o, const void* proj, in
     else if (proj_dtype == RB_F32 && out_dtype == RB_F32) RB_GNG(float, float, bf);
     else return RB_ERR_BAD_DTYPE;
 #undef RB_GNG
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// The same recurrence for prompts, by blocks of 64 tokens that run side by side (see above).  work: float32
+// [blocks, heads, dim, vdim] with blocks >= the sum over the sequences of ceil(tokens / 64) (at most T / 64 + B).
+// Head sizes up to 128; beyond, RB_ERR_BAD_SIZE (the caller then takes rb_decay_scan).
+extern "C" int rb_decay_scan_blocks(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_off,
+                                    int k_off, int v_off, int heads, int dim, int vdim, int act_qk, int act_v,
+                                    float k_scale, const float* decay, float* state, const int* seq_slot, const int* cu_q,
+                                    int B, int max_blocks, float* work, float* out, int ld_out, void* stream) {
+    if (B <= 0 || max_blocks <= 0) return RB_OK;
+    if (heads <= 0 || dim <= 0 || vdim <= 0 || dim > 128 || vdim > 128 || n_in < 1 || B > 65535 || heads > 65535)
+        return RB_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem1 = (size_t)CB * (dim + vdim) * sizeof(float);
+    const size_t smem3 = ((size_t)2 * CB * (dim + 1) + (size_t)CB * vdim + (size_t)CB * (CB + 1)) * sizeof(float);
+    const bool small = dim <= 64 && vdim <= 64;
+    dim3 grid(max_blocks, heads);
+#define RB_BLOCKS(IT, R)                                                                                                  \
+    do {                                                                                                                  \
+        cudaError_t e = cudaFuncSetAttribute(chunk_state_kernel<IT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1); \
+        if (e != cudaSuccess) return (int)e;                                                                              \
+        e = cudaFuncSetAttribute(chunk_out_kernel<IT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);       \
+        if (e != cudaSuccess) return (int)e;                                                                              \
+        RB_LAUNCH((chunk_state_kernel<IT, R>), grid, dim3(CT), smem1, s, (const IT*)in, n_in, (size_t)in_stride, row_stride, \
+                  k_off, v_off, heads, dim, vdim, act_qk, act_v, k_scale, decay, seq_slot, cu_q, B, work);                \
+        RB_LAUNCH((chunk_prefix_kernel), dim3((dim * vdim + 255) / 256, heads, B), dim3(256), 0, s, decay, state, seq_slot, \
+                  cu_q, B, heads, dim, vdim, work);                                                                       \
+        RB_LAUNCH((chunk_out_kernel<IT, R>), grid, dim3(CT), smem3, s, (const IT*)in, n_in, (size_t)in_stride, row_stride, \
+                  q_off, k_off, v_off, heads, dim, vdim, act_qk, act_v, k_scale, decay, seq_slot, cu_q, B, work, out, ld_out); \
+    } while (0)
+    if (in_dtype == RB_BF16) { if (small) RB_BLOCKS(__nv_bfloat16, 4); else RB_BLOCKS(__nv_bfloat16, 8); }
+    else if (in_dtype == RB_F32) { if (small) RB_BLOCKS(float, 4); else RB_BLOCKS(float, 8); }
+    else return RB_ERR_BAD_DTYPE;
+#undef RB_BLOCKS
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

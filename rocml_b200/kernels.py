@@ -173,6 +173,8 @@ def _lib():
         lib.rb_head_gate.argtypes = [_vp, _ll, _i, _vp, _ll, _i, _vp, _i, _i, _i, _vp]
         lib.rb_decay_scan.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _i,
                                       _vp, _i, _vp]
+        lib.rb_decay_scan_blocks.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _i,
+                                             _i, _vp, _vp, _i, _vp]
         lib.rb_group_norm_gate.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _i, _f, _i, _i, _i, _vp, _i, _i, _vp,
                                            _i, _vp]
         lib.rb_gemm_tcgen05_set_wait.argtypes = [_ll, _i]
@@ -1114,6 +1116,40 @@ def decay_scan(proj: torch.Tensor, n_tokens: int, q_off: int, k_off: int, v_off:
                               dim, vdim, UNIT_ACTS[qk_act], UNIT_ACTS[v_act], float(k_scale), _ptr(decay), _ptr(state),
                               _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), n_seqs, _ptr(out), out.stride(0), _stream())
     _check(rc, "decay_scan")
+
+
+DECAY_BLOCK = 64        # tokens a block of decay_scan_blocks
+DECAY_BLOCKS_MAX_HEAD = 128
+
+
+@_profiled(lambda a, facts: _cost.decay_scan(a["n_tokens"], a["n_seqs"], a["heads"], a["dim"], a["vdim"], _n_in(a["proj"]),
+                                             _esz(a["proj"])))
+def decay_scan_blocks(proj: torch.Tensor, n_tokens: int, q_off: int, k_off: int, v_off: int, heads: int, dim: int, vdim: int,
+                      qk_act: str, v_act: str, k_scale: float, decay: torch.Tensor, state: torch.Tensor,
+                      seq_slot: torch.Tensor, cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor, work: torch.Tensor) -> bool:
+    """``decay_scan`` for prompts: blocks of 64 tokens run side by side (each block's own sum, the states the blocks
+    start from along every sequence, each block's outputs).  ``work``: float32 [blocks, heads, dim, vdim] with
+    blocks >= n_tokens // 64 + n_seqs.  False, and nothing launched, for head sizes beyond 128."""
+    if dim > DECAY_BLOCKS_MAX_HEAD or vdim > DECAY_BLOCKS_MAX_HEAD:
+        return False
+    n_in, in_stride, row_stride = _partials(proj, "decay_scan_blocks")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError("decay_scan_blocks: state must be contiguous float32 [slots, heads, dim, vdim]")
+    if decay.dtype != torch.float32 or decay.numel() != heads or not decay.is_contiguous():
+        raise KernelError("decay_scan_blocks: decay must be float32 [heads]")
+    if out.dtype != torch.float32 or out.stride(-1) != 1 or out.shape[-1] != heads * vdim or out.shape[0] < n_tokens:
+        raise KernelError("decay_scan_blocks: out must be float32 [T, heads * vdim]")
+    if max(q_off, k_off) + heads * dim > proj.shape[-1] or v_off + heads * vdim > proj.shape[-1]:
+        raise KernelError("decay_scan_blocks: the projection rows are too narrow")
+    if work.dtype != torch.float32 or not work.is_contiguous() or tuple(work.shape[1:]) != (heads, dim, vdim) or \
+            work.shape[0] < n_tokens // DECAY_BLOCK + n_seqs:
+        raise KernelError("decay_scan_blocks: work must be float32 [n_tokens // 64 + n_seqs, heads, dim, vdim]")
+    rc = _lib().rb_decay_scan_blocks(_ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, q_off, k_off, v_off,
+                                     heads, dim, vdim, UNIT_ACTS[qk_act], UNIT_ACTS[v_act], float(k_scale), _ptr(decay),
+                                     _ptr(state), _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), n_seqs, work.shape[0],
+                                     _ptr(work), _ptr(out), out.stride(0), _stream())
+    _check(rc, "decay_scan_blocks")
+    return True
 
 
 @_profiled(lambda a, facts: (a["n_tokens"] * a["o"].shape[1] * (4 + _esz(a["proj"]) * _n_in(a["proj"]) + _esz(a["out"])),

@@ -9,8 +9,9 @@
 
 What a sequence keeps is the state alone (``StateRequirement``: [heads, head_dim, v_head_dim] in 32-bit),
 whatever its length.  One stacked product makes q | k | v | gate from the layer's input; one kernel
-carries the step's tokens through the recurrence (prompts, pieces of prompts and single tokens alike,
-from the state the step before left); one kernel normalises and gates; the output product is the one
+carries the step's tokens through the recurrence token after token (single tokens and short pieces), or three
+kernels do the same by blocks of 64 tokens that run side by side (prompts), both from the state the step before
+left; one kernel normalises and gates; the output product is the one
 every mixer uses.  From the projections on everything is 32-bit: decays, state, sums, the norm, the gate.
 Two designs differ only in the parameters: lightning attention (silu on q, k, v; one norm with a weight over
 all heads; sigmoid gate) and retention (no activation; k / sqrt(head_dim); a norm per head without weight;
@@ -32,6 +33,10 @@ from .base import BuildEnv, DeferredNorm, Mixer, register_mixer
 from .linear import Linear
 
 TENSOR_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "gate": "g_proj", "o": "o_proj", "out_norm": "out_norm"}
+
+# A step whose longest sequence brings more tokens than this runs the recurrence by blocks of 64 tokens side by side
+# (three kernels); up to it, token after token in one kernel (also every decode step).
+BLOCKS_MIN_TOKENS = 16
 
 
 @register_mixer("linear_attention")
@@ -98,7 +103,8 @@ class LinearAttention(Mixer):
         esz = 4 if self.env.mode == "float32" else 2
         parts = 8 if n_tokens <= 128 else 1
         vw = self.heads * self.vd
-        return n_tokens * (self.proj.n * max(esz, 4 * parts if parts > 1 else esz) + vw * (4 + esz) + self.hidden * 4 * parts)
+        blocks = (n_tokens // 64 + 8) * self.heads * self.hd * self.vd * 4 if n_tokens > BLOCKS_MIN_TOKENS else 0
+        return n_tokens * (self.proj.n * max(esz, 4 * parts if parts > 1 else esz) + vw * (4 + esz) + self.hidden * 4 * parts) + blocks
 
     def cost(self, q_lens, kv_lens):
         from ..profile import cost as C
@@ -120,8 +126,17 @@ class LinearAttention(Mixer):
         q_off, k_off, v_off, g_off = self.offsets
         o = torch.empty((T, vw), dtype=torch.float32, device=dev)
         with scope(op="decay_scan"):
-            kernels.decay_scan(proj, T, q_off, k_off, v_off, self.heads, self.hd, self.vd, self.qk_act, self.v_act,
-                               self.k_scale, self.decay, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, o)
+            done = False
+            if not batch.is_decode and batch.max_q_len > BLOCKS_MIN_TOKENS and max(self.hd, self.vd) <= kernels.DECAY_BLOCKS_MAX_HEAD:
+                # prompts: blocks of 64 tokens side by side instead of one token after another
+                work = torch.empty((T // kernels.DECAY_BLOCK + batch.n_seqs, self.heads, self.hd, self.vd),
+                                   dtype=torch.float32, device=dev)
+                done = kernels.decay_scan_blocks(proj, T, q_off, k_off, v_off, self.heads, self.hd, self.vd, self.qk_act,
+                                                 self.v_act, self.k_scale, self.decay, view.state, batch.seq_slot,
+                                                 batch.cu_q, batch.n_seqs, o, work)
+            if not done:
+                kernels.decay_scan(proj, T, q_off, k_off, v_off, self.heads, self.hd, self.vd, self.qk_act, self.v_act,
+                                   self.k_scale, self.decay, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, o)
         y = torch.empty((T, vw), dtype=act, device=dev)
         with scope(op="out_norm_gate"):
             kernels.group_norm_gate(o, proj, g_off, self.norm_w, self.norm_eps,

@@ -213,6 +213,56 @@ def test_decayed_running_sum(dtype, heads, dim, vdim, acts, k_scale):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, dim, vdim, acts, k_scale", [(3, 16, 24, "silu", 1.0), (2, 24, 8, "none", 24 ** -0.5),
+                                                             (7, 4, 4, "silu", 1.0), (2, 72, 120, "silu", 1.0),
+                                                             (4, 128, 128, "none", 0.1), (2, 64, 64, "silu", 1.0)])
+def test_decayed_running_sum_by_blocks_of_tokens(dtype, heads, dim, vdim, acts, k_scale):
+    """The prompts' way: blocks of 64 tokens side by side, against the plain implementation and against the kernel that
+    goes token after token; sequences of 1, 64, 65, 200 and 131 tokens, one of them going on from a state; a padding
+    entry; decays of 0 and 1."""
+    from rocml_b200 import kernels
+    torch.manual_seed(heads * dim + vdim + 1)
+    dt = DT[dtype]
+    lens = [1, 64, 65, 200, 131]
+    decay = [0.0, 1.0, 0.9, 0.5, 0.99, 0.97, 0.3][:heads]
+    qk, vw = heads * dim, heads * vdim
+    N = 2 * qk + 2 * vw
+    rows = [torch.randn(n, N).to(dt) for n in lens]
+    slots = [3, 0, 5, 1, 4]
+    start = torch.randn(heads, dim, vdim)
+    d_dev = torch.tensor(decay, dtype=torch.float32, device=DEV)
+    x = torch.cat(rows).to(DEV)
+    T = sum(lens)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    ss = torch.tensor(slots[:2] + [-1] + slots[2:], dtype=torch.int32, device=DEV)
+    cu_t = torch.tensor(cu[:3] + [cu[2]] + cu[3:], dtype=torch.int32, device=DEV)
+    got = {}
+    for way in ("blocks", "tokens"):
+        state = torch.zeros((6, heads, dim, vdim), dtype=torch.float32, device=DEV)
+        state[1] = start.to(DEV)
+        o = torch.full((T, vw), float("nan"), dtype=torch.float32, device=DEV)
+        if way == "blocks":
+            work = torch.empty((T // 64 + 6, heads, dim, vdim), dtype=torch.float32, device=DEV)
+            assert kernels.decay_scan_blocks(x, T, 0, qk, 2 * qk, heads, dim, vdim, acts, acts, k_scale, d_dev, state, ss, cu_t, 6, o, work)
+        else:
+            kernels.decay_scan(x, T, 0, qk, 2 * qk, heads, dim, vdim, acts, acts, k_scale, d_dev, state, ss, cu_t, 6, o)
+        got[way] = (o.cpu(), state.cpu())
+    act = P.silu if acts == "silu" else (lambda z: z)
+    for i, r in enumerate(rows):
+        xx = r.double()
+        q = act(xx[:, :qk]).reshape(-1, heads, dim)
+        k = act(xx[:, qk:2 * qk]).reshape(-1, heads, dim) * k_scale
+        v = act(xx[:, 2 * qk:2 * qk + vw]).reshape(-1, heads, vdim)
+        ow, S = P.decayed_sum(q, k, v, decay, state=start.double() if slots[i] == 1 else None)
+        for way in ("blocks", "tokens"):
+            assert close(got[way][0][cu[i]:cu[i + 1]], ow.reshape(-1, vw), 3e-5), (way, i)
+            assert close(got[way][1][slots[i]], S, 3e-5), (way, i)
+    assert float(got["blocks"][1][2].abs().max()) == 0          # a slot that no sequence of the step holds
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("groups, gw, weight, gate", [(1, 72, True, "sigmoid"), (6, 8, False, "silu"), (3, 136, True, "silu"),
                                                       (1, 1000, False, "sigmoid"), (40, 4, False, "sigmoid")])
 def test_norm_over_groups_of_columns_and_gate(dtype, groups, gw, weight, gate):
