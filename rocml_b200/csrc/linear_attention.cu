@@ -160,7 +160,7 @@ __device__ __forceinline__ void stage_rows(const IT* in, int n_in, size_t in_str
 }
 
 template <typename IT, int R>
-__global__ void __launch_bounds__(CT)
+__global__ void __launch_bounds__(CT, 2)
 chunk_state_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int k_off, int v_off, int heads,
                    int dim, int vdim, int act_qk, int act_v, float k_scale, const float* __restrict__ decay,
                    const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int B, float* __restrict__ Lbuf) {
@@ -204,6 +204,10 @@ chunk_state_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int ro
             if (ty + 16 * a < dim && tx + 16 * c < vdim) L[(size_t)(ty + 16 * a) * vdim + tx + 16 * c] = acc[a][c];
 }
 
+// A thread owns V neighbouring entries of the state (V = 4 where the state's size allows 16-byte accesses) and walks the
+// sequence's blocks in order; the loads of eight blocks are in flight together (they do not depend on the running
+// state), so the walk is not one memory latency a block.
+template <int V>
 __global__ void __launch_bounds__(256)
 chunk_prefix_kernel(const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ seq_slot,
                     const int* __restrict__ cu_q, int B, int heads, int dim, int vdim, float* __restrict__ Lbuf) {
@@ -217,25 +221,36 @@ chunk_prefix_kernel(const float* __restrict__ decay, float* __restrict__ state, 
     int first = 0;
     for (int i = 0; i < b; ++i)
         if (seq_slot[i] >= 0) first += (cu_q[i + 1] - cu_q[i] + CB - 1) / CB;
-    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int e = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (e >= dim * vdim) return;
     const float d = decay[h];
     const float d_full = decay_pow(d, CB);
-    float* st = state + ((size_t)slot * heads + h) * dim * vdim + e;
-    float run = *st;
+    struct alignas(4 * V) Vec { float x[V]; };
+    const size_t sz = (size_t)dim * vdim;
+    Vec* st = reinterpret_cast<Vec*>(state + ((size_t)slot * heads + h) * sz + e);
+    Vec run = *st;
     const int nb = (n + CB - 1) / CB;
-    for (int c = 0; c < nb; ++c) {
-        float* L = Lbuf + ((size_t)(first + c) * heads + h) * dim * vdim + e;
-        const float own = *L;
-        *L = run;                                             // the state this block of tokens starts from
-        const int m = min(CB, n - c * CB);
-        run = fmaf(m == CB ? d_full : decay_pow(d, m), run, own);
+    constexpr int U = 8;
+    for (int c0 = 0; c0 < nb; c0 += U) {
+        Vec own[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (c0 + u < nb) own[u] = *reinterpret_cast<const Vec*>(Lbuf + ((size_t)(first + c0 + u) * heads + h) * sz + e);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (c0 + u >= nb) break;
+            *reinterpret_cast<Vec*>(Lbuf + ((size_t)(first + c0 + u) * heads + h) * sz + e) = run;   // what this block starts from
+            const int m = min(CB, n - (c0 + u) * CB);
+            const float f = m == CB ? d_full : decay_pow(d, m);
+#pragma unroll
+            for (int v = 0; v < V; ++v) run.x[v] = fmaf(f, run.x[v], own[u].x[v]);
+        }
     }
     *st = run;
 }
 
 template <typename IT, int R>
-__global__ void __launch_bounds__(CT)
+__global__ void __launch_bounds__(CT, 2)
 chunk_out_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int q_off, int k_off, int v_off,
                  int heads, int dim, int vdim, int act_qk, int act_v, float k_scale, const float* __restrict__ decay,
                  const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int B, const float* __restrict__ Lbuf,
@@ -248,14 +263,21 @@ chunk_out_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_
     if (!find_block(blockIdx.x, seq_slot, cu_q, B, &b, &t0, &m, &first, &slot)) return;
     const int h = blockIdx.y;
     const float d = decay[h];
-    const int ldq = dim + 1;
-    float* qs = sm;                        // [CB][dim + 1]
-    float* ks = qs + CB * ldq;             // [CB][dim + 1]; later slabs of the starting state
-    float* vs = ks + CB * ldq;             // [CB][vdim]
-    float* A = vs + CB * vdim;             // [CB][CB + 1]
+    // No padding anywhere (two blocks then fit a multiprocessor at head size 128): a warp reads two rows of q and of
+    // A at one column (broadcasts), and 16 neighbouring entries of a row of k^T, v or the state.
+    const int ldq = dim;
+    float* qs = sm;                        // [CB][dim]
+    float* ks = qs + CB * dim;             // k transposed, [dim][CB]; later slabs of the starting state
+    float* vs = ks + CB * dim;             // [CB][vdim]
+    float* A = vs + CB * vdim;             // [CB][CB]
     if (threadIdx.x <= CB) pw[threadIdx.x] = decay_pow(d, threadIdx.x);
     stage_rows(in, n_in, in_stride, row_stride, t0, m, q_off + h * dim, dim, act_qk, qs, ldq, nullptr, 1.f);
-    stage_rows(in, n_in, in_stride, row_stride, t0, m, k_off + h * dim, dim, act_qk, ks, ldq, nullptr, k_scale);
+    for (int idx = threadIdx.x; idx < m * dim; idx += CT) {
+        const int tt = idx / dim, i = idx - tt * dim;
+        float x = load_sum(in + (size_t)(t0 + tt) * row_stride + k_off + h * dim + i, n_in, in_stride);
+        if (act_qk == 1) x = silu(x);
+        ks[i * CB + tt] = x * k_scale;
+    }
     stage_rows(in, n_in, in_stride, row_stride, t0, m, v_off + h * vdim, vdim, act_v, vs, vdim, nullptr, 1.f);
     __syncthreads();
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
@@ -271,7 +293,7 @@ chunk_out_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_
 #pragma unroll
             for (int a = 0; a < 4; ++a) qq[a] = ty + 16 * a < m ? qs[(ty + 16 * a) * ldq + i] : 0.f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) kk[c] = tx + 16 * c < m ? ks[(tx + 16 * c) * ldq + i] : 0.f;
+            for (int c = 0; c < 4; ++c) kk[c] = tx + 16 * c < m ? ks[i * CB + tx + 16 * c] : 0.f;
 #pragma unroll
             for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -282,7 +304,7 @@ chunk_out_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int t = ty + 16 * a, s = tx + 16 * c;
-                A[t * (CB + 1) + s] = (s <= t && t < m) ? acc[a][c] * pw[t - s] : 0.f;
+                A[t * CB + s] = (s <= t && t < m) ? acc[a][c] * pw[t - s] : 0.f;
             }
     }
     __syncthreads();
@@ -295,7 +317,7 @@ chunk_out_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_
     for (int s = 0; s < m; ++s) {
         float aa[4], vv[R];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) aa[a] = A[(ty + 16 * a) * (CB + 1) + s];
+        for (int a = 0; a < 4; ++a) aa[a] = A[(ty + 16 * a) * CB + s];
 #pragma unroll
         for (int c = 0; c < R; ++c) vv[c] = tx + 16 * c < vdim ? vs[s * vdim + tx + 16 * c] : 0.f;
 #pragma unroll
@@ -461,7 +483,7 @@ extern "C" int rb_decay_scan_blocks(const void* in, int in_dtype, int n_in, long
         return RB_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem1 = (size_t)CB * (dim + vdim) * sizeof(float);
-    const size_t smem3 = ((size_t)2 * CB * (dim + 1) + (size_t)CB * vdim + (size_t)CB * (CB + 1)) * sizeof(float);
+    const size_t smem3 = ((size_t)2 * CB * dim + (size_t)CB * vdim + (size_t)CB * CB) * sizeof(float);
     const bool small = dim <= 64 && vdim <= 64;
     dim3 grid(max_blocks, heads);
 #define RB_BLOCKS(IT, R)                                                                                                  \
@@ -472,8 +494,12 @@ extern "C" int rb_decay_scan_blocks(const void* in, int in_dtype, int n_in, long
         if (e != cudaSuccess) return (int)e;                                                                              \
         RB_LAUNCH((chunk_state_kernel<IT, R>), grid, dim3(CT), smem1, s, (const IT*)in, n_in, (size_t)in_stride, row_stride, \
                   k_off, v_off, heads, dim, vdim, act_qk, act_v, k_scale, decay, seq_slot, cu_q, B, work);                \
-        RB_LAUNCH((chunk_prefix_kernel), dim3((dim * vdim + 255) / 256, heads, B), dim3(256), 0, s, decay, state, seq_slot, \
-                  cu_q, B, heads, dim, vdim, work);                                                                       \
+        if ((dim * vdim) % 4 == 0)                                                                                        \
+            RB_LAUNCH((chunk_prefix_kernel<4>), dim3((dim * vdim / 4 + 255) / 256, heads, B), dim3(256), 0, s, decay, state, \
+                      seq_slot, cu_q, B, heads, dim, vdim, work);                                                         \
+        else                                                                                                              \
+            RB_LAUNCH((chunk_prefix_kernel<1>), dim3((dim * vdim + 255) / 256, heads, B), dim3(256), 0, s, decay, state,  \
+                      seq_slot, cu_q, B, heads, dim, vdim, work);                                                         \
         RB_LAUNCH((chunk_out_kernel<IT, R>), grid, dim3(CT), smem3, s, (const IT*)in, n_in, (size_t)in_stride, row_stride, \
                   q_off, k_off, v_off, heads, dim, vdim, act_qk, act_v, k_scale, decay, seq_slot, cu_q, B, work, out, ld_out); \
     } while (0)
