@@ -75,6 +75,10 @@ int rb_moe_combine(const float* y, long long ldy, const int* row_of, const float
 int rb_decay_scan(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_off, int k_off,
                   int v_off, int heads, int dim, int vdim, int act_qk, int act_v, float k_scale, const float* decay,
                   float* state, const int* seq_slot, const int* cu_q, int B, float* out, int ld_out, void* stream);
+// The same for sequences that bring exactly one token each (a decode step): the state streams through registers.
+int rb_decay_step(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_off, int k_off,
+                  int v_off, int heads, int dim, int vdim, int act_qk, int act_v, float k_scale, const float* decay,
+                  float* state, const int* seq_slot, const int* cu_q, int B, float* out, int ld_out, void* stream);
 // The same for prompts, by blocks of 64 tokens that run side by side: work float32 [max_blocks, heads, dim, vdim],
 // max_blocks >= the sum over the sequences of ceil(tokens / 64).  Head sizes up to 128.
 int rb_decay_scan_blocks(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_off, int k_off,

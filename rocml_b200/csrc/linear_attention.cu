@@ -113,6 +113,70 @@ decay_scan_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row
     }
 }
 
+// ---- one token a sequence: the state streams through registers -----------------------------------------------------
+// A block owns a (sequence, head) and 32 of the state's columns; a warp takes every eighth row, a lane a column, so a
+// row's 32 entries are one 128-byte access and nothing of the state passes through shared memory.  Every entry is read,
+// decayed, updated and written once; the warps' sums over their rows meet in shared memory and are added in the
+// order of the warps.
+template <typename IT>
+__global__ void __launch_bounds__(256)
+decay_step_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_stride, int q_off, int k_off, int v_off,
+                  int heads, int dim, int vdim, int act_qk, int act_v, float k_scale, const float* __restrict__ decay,
+                  float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
+                  float* __restrict__ out, int ld_out) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float part[8][32];
+    float* qs = sm;            // [dim]
+    float* ks = sm + dim;      // [dim]
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t = cu_q[b];
+    if (cu_q[b + 1] <= t) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * 32 + lane;
+    const IT* row = in + (size_t)t * row_stride;
+    for (int i = threadIdx.x; i < dim; i += 256) {
+        float q = load_sum(row + q_off + h * dim + i, n_in, in_stride), k = load_sum(row + k_off + h * dim + i, n_in, in_stride);
+        if (act_qk == 1) { q = silu(q); k = silu(k); }
+        qs[i] = q;
+        ks[i] = k * k_scale;
+    }
+    float v = 0.f;
+    if (j < vdim) {
+        v = load_sum(row + v_off + h * vdim + j, n_in, in_stride);
+        if (act_v == 1) v = silu(v);
+    }
+    __syncthreads();
+    const float d = decay[h];
+    float* S = state + (((size_t)slot * heads + h) * dim) * vdim + j;
+    float acc = 0.f;
+    if (j < vdim) {
+        int i = warp;
+        for (; i + 24 < dim; i += 32) {           // four rows' loads in flight
+            float s0 = S[(size_t)i * vdim], s1 = S[(size_t)(i + 8) * vdim], s2 = S[(size_t)(i + 16) * vdim], s3 = S[(size_t)(i + 24) * vdim];
+            s0 = fmaf(ks[i], v, d * s0); s1 = fmaf(ks[i + 8], v, d * s1); s2 = fmaf(ks[i + 16], v, d * s2); s3 = fmaf(ks[i + 24], v, d * s3);
+            S[(size_t)i * vdim] = s0; S[(size_t)(i + 8) * vdim] = s1; S[(size_t)(i + 16) * vdim] = s2; S[(size_t)(i + 24) * vdim] = s3;
+            acc = fmaf(s0, qs[i], acc); acc = fmaf(s1, qs[i + 8], acc); acc = fmaf(s2, qs[i + 16], acc); acc = fmaf(s3, qs[i + 24], acc);
+        }
+        for (; i < dim; i += 8) {
+            const float s = fmaf(ks[i], v, d * S[(size_t)i * vdim]);
+            S[(size_t)i * vdim] = s;
+            acc = fmaf(s, qs[i], acc);
+        }
+    }
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && j < vdim) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) o += part[w][lane];
+        out[(size_t)t * ld_out + (size_t)h * vdim + j] = o;
+    }
+}
+
 // ---- prompts: the same sums by blocks of 64 tokens, all blocks at once ----------------------------------------------
 // Within a block of m tokens that starts from the state S0:
 //   o_t   = d^(t+1) S0^T q_t + sum_{s <= t} d^(t-s) (q_t . k_s) v_s           t = 0 .. m-1
@@ -507,6 +571,29 @@ extern "C" int rb_decay_scan_blocks(const void* in, int in_dtype, int n_in, long
     else if (in_dtype == RB_F32) { if (small) RB_BLOCKS(float, 4); else RB_BLOCKS(float, 8); }
     else return RB_ERR_BAD_DTYPE;
 #undef RB_BLOCKS
+    RB_LAUNCH_CHECK();
+    return RB_OK;
+}
+
+// One token a sequence (a decode step): rb_decay_scan's result for sequences that bring exactly one token, with the
+// state streamed through registers instead of staged in shared memory.
+extern "C" int rb_decay_step(const void* in, int in_dtype, int n_in, long long in_stride, int row_stride, int q_off,
+                             int k_off, int v_off, int heads, int dim, int vdim, int act_qk, int act_v, float k_scale,
+                             const float* decay, float* state, const int* seq_slot, const int* cu_q, int B, float* out,
+                             int ld_out, void* stream) {
+    if (B <= 0) return RB_OK;
+    if (heads <= 0 || dim <= 0 || vdim <= 0 || n_in < 1 || B > 65535 || heads > 65535 || dim > 4096) return RB_ERR_BAD_SIZE;
+    dim3 grid((vdim + 31) / 32, heads, B);
+    const size_t smem = (size_t)2 * dim * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (in_dtype == RB_BF16)
+        RB_LAUNCH((decay_step_kernel<__nv_bfloat16>), grid, dim3(256), smem, s, (const __nv_bfloat16*)in, n_in, (size_t)in_stride,
+                  row_stride, q_off, k_off, v_off, heads, dim, vdim, act_qk, act_v, k_scale, decay, state, seq_slot, cu_q, out, ld_out);
+    else if (in_dtype == RB_F32)
+        RB_LAUNCH((decay_step_kernel<float>), grid, dim3(256), smem, s, (const float*)in, n_in, (size_t)in_stride, row_stride,
+                  q_off, k_off, v_off, heads, dim, vdim, act_qk, act_v, k_scale, decay, state, seq_slot, cu_q, out, ld_out);
+    else
+        return RB_ERR_BAD_DTYPE;
     RB_LAUNCH_CHECK();
     return RB_OK;
 }

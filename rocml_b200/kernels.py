@@ -173,6 +173,7 @@ def _lib():
         lib.rb_head_gate.argtypes = [_vp, _ll, _i, _vp, _ll, _i, _vp, _i, _i, _i, _vp]
         lib.rb_decay_scan.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _i,
                                       _vp, _i, _vp]
+        lib.rb_decay_step.argtypes = lib.rb_decay_scan.argtypes
         lib.rb_decay_scan_blocks.argtypes = [_vp, _i, _i, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _i,
                                              _i, _vp, _vp, _i, _vp]
         lib.rb_group_norm_gate.argtypes = [_vp, _i, _vp, _i, _i, _ll, _i, _i, _vp, _i, _f, _i, _i, _i, _vp, _i, _i, _vp,
@@ -1097,8 +1098,10 @@ UNIT_ACTS = {"none": 0, "silu": 1, "sigmoid": 2}
                                              _esz(a["proj"])))
 def decay_scan(proj: torch.Tensor, n_tokens: int, q_off: int, k_off: int, v_off: int, heads: int, dim: int, vdim: int,
                qk_act: str, v_act: str, k_scale: float, decay: torch.Tensor, state: torch.Tensor, seq_slot: torch.Tensor,
-               cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor):
-    """The step's tokens through S = decay[h] * S + k v^T, o = S^T q for every (sequence, head).  ``proj`` [T, N] (or
+               cu_q: torch.Tensor, n_seqs: int, out: torch.Tensor, one_token_each: bool = False):
+    """The step's tokens through S = decay[h] * S + k v^T, o = S^T q for every (sequence, head).
+    ``one_token_each``: every sequence brings exactly one token (a decode step); the kernel then streams the state
+    through registers instead of staging it in shared memory (rounding differs, nothing else).  ``proj`` [T, N] (or
     [S, T, N] float32 partial sums) holds q and k (heads * dim columns from q_off and k_off) and v (heads * vdim from
     v_off); ``qk_act`` / ``v_act``: "none" or "silu"; k is multiplied by ``k_scale``.  ``state`` float32
     [slots, heads, dim, vdim] is read and written in place for the slots of ``seq_slot``; ``out`` float32
@@ -1112,9 +1115,10 @@ def decay_scan(proj: torch.Tensor, n_tokens: int, q_off: int, k_off: int, v_off:
         raise KernelError("decay_scan: out must be float32 [T, heads * vdim]")
     if max(q_off, k_off) + heads * dim > proj.shape[-1] or v_off + heads * vdim > proj.shape[-1]:
         raise KernelError("decay_scan: the projection rows are too narrow")
-    rc = _lib().rb_decay_scan(_ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, q_off, k_off, v_off, heads,
-                              dim, vdim, UNIT_ACTS[qk_act], UNIT_ACTS[v_act], float(k_scale), _ptr(decay), _ptr(state),
-                              _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), n_seqs, _ptr(out), out.stride(0), _stream())
+    fn = _lib().rb_decay_step if one_token_each else _lib().rb_decay_scan
+    rc = fn(_ptr(proj), dtype_code(proj.dtype), n_in, in_stride, row_stride, q_off, k_off, v_off, heads,
+            dim, vdim, UNIT_ACTS[qk_act], UNIT_ACTS[v_act], float(k_scale), _ptr(decay), _ptr(state),
+            _i32(seq_slot, "seq_slot"), _i32(cu_q, "cu_q"), n_seqs, _ptr(out), out.stride(0), _stream())
     _check(rc, "decay_scan")
 
 

@@ -136,7 +136,8 @@ class LinearAttention(Mixer):
                                                  batch.cu_q, batch.n_seqs, o, work)
             if not done:
                 kernels.decay_scan(proj, T, q_off, k_off, v_off, self.heads, self.hd, self.vd, self.qk_act, self.v_act,
-                                   self.k_scale, self.decay, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, o)
+                                   self.k_scale, self.decay, view.state, batch.seq_slot, batch.cu_q, batch.n_seqs, o,
+                                   one_token_each=batch.is_decode)
         y = torch.empty((T, vw), dtype=act, device=dev)
         with scope(op="out_norm_gate"):
             kernels.group_norm_gate(o, proj, g_off, self.norm_w, self.norm_eps,

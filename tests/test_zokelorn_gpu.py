@@ -262,6 +262,43 @@ def test_decayed_running_sum_by_blocks_of_tokens(dtype, heads, dim, vdim, acts, 
     assert float(got["blocks"][1][2].abs().max()) == 0          # a slot that no sequence of the step holds
 
 
+@pytest.mark.parametrize("heads, dim, vdim, acts", [(3, 16, 24, "silu"), (2, 24, 8, "none"), (7, 4, 4, "silu"), (2, 72, 136, "silu"),
+                                                   (4, 128, 128, "none"), (1, 300, 40, "none")])
+def test_decayed_running_sum_one_token_a_sequence(heads, dim, vdim, acts):
+    """A decode step's kernel: twenty steps of four sequences (one entry of the batch is padding) from given states,
+    from partial sums, against the plain implementation; decays of 0 and 1."""
+    from rocml_b200 import kernels
+    torch.manual_seed(heads * dim + vdim + 2)
+    steps, B = 20, 4
+    decay = [0.0, 1.0, 0.9, 0.5, 0.99, 0.97, 0.3][:heads]
+    qk, vw = heads * dim, heads * vdim
+    N = 2 * qk + vw
+    rows = torch.randn(steps, 2, B, N)                       # two partial sums a step
+    start = torch.randn(B, heads, dim, vdim)
+    state = torch.zeros((6, heads, dim, vdim), dtype=torch.float32, device=DEV)
+    slots = [5, 0, 3, 2]
+    for i, s in enumerate(slots):
+        state[s] = start[i].to(DEV)
+    d_dev = torch.tensor(decay, dtype=torch.float32, device=DEV)
+    ss = torch.tensor(slots[:2] + [-1] + slots[2:], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 1, 2, 2, 3, 4], dtype=torch.int32, device=DEV)
+    got = []
+    for t in range(steps):
+        o = torch.full((B, vw), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.decay_scan(rows[t].to(DEV), B, 0, qk, 2 * qk, heads, dim, vdim, acts, acts, 0.5, d_dev, state, ss, cu, 5, o,
+                           one_token_each=True)
+        got.append(o.cpu())
+    got = torch.stack(got)                                   # [steps, B, vw]
+    act = P.silu if acts == "silu" else (lambda z: z)
+    for i in range(B):
+        x = rows[:, :, i].double().sum(1)
+        ow, S = P.decayed_sum(act(x[:, :qk]).reshape(-1, heads, dim), act(x[:, qk:2 * qk]).reshape(-1, heads, dim) * 0.5,
+                              act(x[:, 2 * qk:]).reshape(-1, heads, vdim), decay, state=start[i].double())
+        assert close(got[:, i], ow.reshape(steps, vw), 3e-5), i
+        assert close(state[slots[i]], S, 3e-5), i
+    assert float(state[1].abs().max()) == 0 and float(state[4].abs().max()) == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("groups, gw, weight, gate", [(1, 72, True, "sigmoid"), (6, 8, False, "silu"), (3, 136, True, "silu"),
                                                       (1, 1000, False, "sigmoid"), (40, 4, False, "sigmoid")])
