@@ -212,14 +212,54 @@ __device__ __forceinline__ bool find_block(int g, const int* seq_slot, const int
     return false;
 }
 
-template <typename IT>
+// m rows of `width` columns from column col0 of the projection rows into shared memory as 32-bit numbers (partial sums
+// added, the activation applied, times factor and the row's own factor); TR: transposed, dst[column][row].  16 bytes a
+// load where the columns and strides allow.
+template <typename IT, bool TR>
 __device__ __forceinline__ void stage_rows(const IT* in, int n_in, size_t in_stride, int row_stride, int t0, int m, int col0,
                                            int width, int act, float* dst, int ld, const float* row_factor, float factor) {
+    constexpr int V = sizeof(IT) == 2 ? 8 : 4;
+    const bool vec = width % V == 0 && row_stride % V == 0 && col0 % V == 0 && in_stride % V == 0 && ((uintptr_t)in & 15) == 0;
+    if (vec) {
+        const int wv = width / V;
+        for (int idx = threadIdx.x; idx < m * wv; idx += CT) {
+            const int tt = idx / wv, i0 = (idx - tt * wv) * V;
+            const IT* p = in + (size_t)(t0 + tt) * row_stride + col0 + i0;
+            float x[V];
+#pragma unroll
+            for (int u = 0; u < V; ++u) x[u] = 0.f;
+            for (int s = 0; s < n_in; ++s) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(p + (size_t)s * in_stride);
+                if (sizeof(IT) == 2) {
+                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        x[2 * u] += __uint_as_float(w[u] << 16);
+                        x[2 * u + 1] += __uint_as_float(w[u] & 0xFFFF0000u);
+                    }
+                } else {
+                    x[0] += __uint_as_float(raw.x); x[1] += __uint_as_float(raw.y);
+                    x[2] += __uint_as_float(raw.z); x[3] += __uint_as_float(raw.w);
+                }
+            }
+            const float f = factor * (row_factor ? row_factor[tt] : 1.f);
+#pragma unroll
+            for (int u = 0; u < V; ++u) {
+                float y = x[u];
+                if (act == 1) y = silu(y);
+                if (TR) dst[(i0 + u) * ld + tt] = y * f;
+                else dst[tt * ld + i0 + u] = y * f;
+            }
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < m * width; idx += CT) {
         const int tt = idx / width, i = idx - tt * width;
         float x = load_sum(in + (size_t)(t0 + tt) * row_stride + col0 + i, n_in, in_stride);
         if (act == 1) x = silu(x);
-        dst[tt * ld + i] = x * factor * (row_factor ? row_factor[tt] : 1.f);
+        x *= factor * (row_factor ? row_factor[tt] : 1.f);
+        if (TR) dst[i * ld + tt] = x;
+        else dst[tt * ld + i] = x;
     }
 }
 
@@ -240,8 +280,8 @@ chunk_state_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int ro
     float* vs = ks + CB * dim;            // [m][vdim]
     if (threadIdx.x < m) pw[threadIdx.x] = decay_pow(d, m - 1 - threadIdx.x);
     __syncthreads();
-    stage_rows(in, n_in, in_stride, row_stride, t0, m, k_off + h * dim, dim, act_qk, ks, dim, pw, k_scale);
-    stage_rows(in, n_in, in_stride, row_stride, t0, m, v_off + h * vdim, vdim, act_v, vs, vdim, nullptr, 1.f);
+    stage_rows<IT, false>(in, n_in, in_stride, row_stride, t0, m, k_off + h * dim, dim, act_qk, ks, dim, pw, k_scale);
+    stage_rows<IT, false>(in, n_in, in_stride, row_stride, t0, m, v_off + h * vdim, vdim, act_v, vs, vdim, nullptr, 1.f);
     __syncthreads();
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     float acc[R][R];
@@ -335,14 +375,9 @@ chunk_out_kernel(const IT* __restrict__ in, int n_in, size_t in_stride, int row_
     float* vs = ks + CB * dim;             // [CB][vdim]
     float* A = vs + CB * vdim;             // [CB][CB]
     if (threadIdx.x <= CB) pw[threadIdx.x] = decay_pow(d, threadIdx.x);
-    stage_rows(in, n_in, in_stride, row_stride, t0, m, q_off + h * dim, dim, act_qk, qs, ldq, nullptr, 1.f);
-    for (int idx = threadIdx.x; idx < m * dim; idx += CT) {
-        const int tt = idx / dim, i = idx - tt * dim;
-        float x = load_sum(in + (size_t)(t0 + tt) * row_stride + k_off + h * dim + i, n_in, in_stride);
-        if (act_qk == 1) x = silu(x);
-        ks[i * CB + tt] = x * k_scale;
-    }
-    stage_rows(in, n_in, in_stride, row_stride, t0, m, v_off + h * vdim, vdim, act_v, vs, vdim, nullptr, 1.f);
+    stage_rows<IT, false>(in, n_in, in_stride, row_stride, t0, m, q_off + h * dim, dim, act_qk, qs, ldq, nullptr, 1.f);
+    stage_rows<IT, true>(in, n_in, in_stride, row_stride, t0, m, k_off + h * dim, dim, act_qk, ks, CB, nullptr, k_scale);
+    stage_rows<IT, false>(in, n_in, in_stride, row_stride, t0, m, v_off + h * vdim, vdim, act_v, vs, vdim, nullptr, 1.f);
     __syncthreads();
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     {
