@@ -618,6 +618,24 @@ __global__ void head_gate_kernel(const AT* __restrict__ in, long long ld_in, int
                                  int out_w, const float* __restrict__ gate, int heads, int T) {
     pdl_trigger();
     pdl_wait();
+    if ((in_w & 3) == 0 && (out_w & 3) == 0 && (ld_in & 3) == 0 && (ld_out & 3) == 0 &&
+        (((uintptr_t)in | (uintptr_t)out) & (4 * sizeof(AT) - 1)) == 0) {
+        // four neighbouring values a thread
+        const int w4 = out_w >> 2;
+        const size_t n4 = (size_t)T * heads * w4;
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n4; idx += (size_t)gridDim.x * blockDim.x) {
+            const size_t th = idx / w4;
+            const int d = (int)(idx - th * w4) * 4;
+            const size_t t = th / heads;
+            const int h = (int)(th - t * heads);
+            const float g = gate ? gate[th] : 1.f;
+            float x[4];
+            load4(in + t * ld_in + (size_t)h * in_w + d, x);
+            x[0] *= g; x[1] *= g; x[2] *= g; x[3] *= g;
+            store4(out + t * ld_out + (size_t)h * out_w + d, x);
+        }
+        return;
+    }
     const size_t n = (size_t)T * heads * out_w;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t th = idx / out_w;

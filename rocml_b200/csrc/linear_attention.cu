@@ -470,6 +470,39 @@ group_norm_gate_kernel(const float* __restrict__ o, int ld_o, const IT* __restri
     AT* dst = out + (size_t)t * ld_out;
     const int gw = W / groups;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    // four columns a thread where sizes and addresses allow: a warp a group (or the whole block the one group)
+    if ((gw & 3) == 0 && (ld_o & 3) == 0 && (row_stride & 3) == 0 && (g_off & 3) == 0 && (in_stride & 3) == 0 && (ld_out & 3) == 0 &&
+        ((uintptr_t)o & 15) == 0 && ((uintptr_t)proj & (4 * sizeof(IT) - 1)) == 0 && ((uintptr_t)out & (4 * sizeof(AT) - 1)) == 0 &&
+        (!w || ((uintptr_t)w & (4 * sizeof(WT) - 1)) == 0)) {
+        const int first = groups == 1 ? 0 : warp, step_g = groups == 1 ? 1 : nwarps;
+        const int me = groups == 1 ? threadIdx.x : lane, n_me = groups == 1 ? blockDim.x : 32;
+        for (int gi = first; gi < groups; gi += step_g) {
+            float ss = 0.f;
+            for (int i = me * 4; i < gw; i += n_me * 4) {
+                float x[4];
+                load4(row + gi * gw + i, x);
+                ss += x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+            }
+            ss = groups == 1 ? block_sum(ss, scratch) : warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)gw + eps);
+            for (int i = me * 4; i < gw; i += n_me * 4) {
+                const int c = gi * gw + i;
+                float x[4], z[4] = {0.f, 0.f, 0.f, 0.f}, ww[4] = {1.f, 1.f, 1.f, 1.f};
+                load4(row + c, x);
+                for (int s = 0; s < n_in; ++s) {
+                    float p[4];
+                    load4(g + (size_t)s * in_stride + c, p);
+                    z[0] += p[0]; z[1] += p[1]; z[2] += p[2]; z[3] += p[3];
+                }
+                if (w) load4(w + c, ww);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    x[u] = x[u] * inv * ww[u] * (gate_act == 1 ? silu(z[u]) : (gate_act == 2 ? 1.f / (1.f + expf(-z[u])) : 1.f));
+                store4(dst + c, x);
+            }
+        }
+        return;
+    }
     if (groups == 1) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < W; i += blockDim.x) { const float x = row[i]; ss += x * x; }

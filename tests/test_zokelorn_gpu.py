@@ -301,7 +301,8 @@ def test_decayed_running_sum_one_token_a_sequence(heads, dim, vdim, acts):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("groups, gw, weight, gate", [(1, 72, True, "sigmoid"), (6, 8, False, "silu"), (3, 136, True, "silu"),
-                                                      (1, 1000, False, "sigmoid"), (40, 4, False, "sigmoid")])
+                                                      (1, 1000, False, "sigmoid"), (40, 4, False, "sigmoid"),
+                                                      (5, 6, True, "silu"), (1, 30, True, "sigmoid")])
 def test_norm_over_groups_of_columns_and_gate(dtype, groups, gw, weight, gate):
     from rocml_b200 import kernels
     torch.manual_seed(groups + gw)
@@ -395,13 +396,15 @@ def test_gelu_gate_and_head_gate(dtype):
     kernels.gated_act(gu.to(DEV), out, "gelu_tanh")
     x = gu.double().sum(0)
     assert close(out, P.gelu_tanh(x[:, :I]) * x[:, I:], 1e-6 if dtype == "float32" else 1e-2)
-    heads, in_w, out_w = 5, 32, 20
-    a = torch.randn(T, heads * in_w).to(dt)
-    g = torch.rand(T, heads)
-    o = torch.empty((T, heads * out_w), dtype=dt, device=DEV)
-    kernels.head_gate(a.to(DEV), o, g.to(DEV), heads, in_w, out_w, T)
-    want = a.double().reshape(T, heads, in_w)[:, :, :out_w] * g.double()[:, :, None]
-    assert close(o, want.reshape(T, -1), 1e-6 if dtype == "float32" else 1e-2)
+    for heads, in_w, out_w in ((5, 32, 20), (3, 30, 18), (2, 128, 128)):
+        a = torch.randn(T, heads * in_w).to(dt)
+        g = torch.rand(T, heads)
+        o = torch.empty((T, heads * out_w), dtype=dt, device=DEV)
+        kernels.head_gate(a.to(DEV), o, g.to(DEV), heads, in_w, out_w, T)
+        want = a.double().reshape(T, heads, in_w)[:, :, :out_w] * g.double()[:, :, None]
+        assert close(o, want.reshape(T, -1), 1e-6 if dtype == "float32" else 1e-2)
+        kernels.head_gate(a.to(DEV), o, None, heads, in_w, out_w, T)
+        assert close(o, a.double().reshape(T, heads, in_w)[:, :, :out_w].reshape(T, -1), 1e-6 if dtype == "float32" else 1e-2)
 
 
 # ---- the engine -----------------------------------------------------------------------------------------------
