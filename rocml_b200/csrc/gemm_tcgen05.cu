@@ -87,7 +87,8 @@ struct Params {
     // stacked B operand), a tile of group -1 is skipped.  b_rows is then one group's feature count.
     const int* tile_group;
     int group_rows;
-    // gated epilogues: 0 silu(g) * u; 1 min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)
+    // gated epilogues: 0 silu(g) * u; 1 min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1);
+    // 2 gelu(g) * u in its tanh form (many tokens only: the few-token kernels apply silu)
     int act_kind;
     float act_limit, act_alpha;
 };
@@ -328,8 +329,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                                 for (int i = 0; i < 16; ++i) { g[i] += p.bias[f0 + i]; u[i] += p.bias[f0 + 16 + i]; }
                             }
+                            if (p.act_kind == 2) {
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                                for (int i = 0; i < 16; ++i) g[i] = rb::gelu_tanh(g[i]) * u[i];
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                            }
                             OT* dst = row + (f0 >> 1);
                             if (vec_ok) store16(dst, g);
                             else {
@@ -635,6 +641,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                         if (p.act_kind == 0) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                        } else if (p.act_kind == 2) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) g[i] = rb::gelu_tanh(g[i]) * u[i];
                         } else {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
@@ -910,8 +919,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                             for (int i = 0; i < 16; ++i) { g[i] += p.bias[f0 + i]; u[i] += p.bias[f0 + 16 + i]; }
                         }
+                        if (p.act_kind == 2) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                            for (int i = 0; i < 16; ++i) g[i] = rb::gelu_tanh(g[i]) * u[i];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+                        }
                         OT* dst = row + (f0 >> 1);
                         if (vec_ok) store16(dst, g);
                         else {
@@ -1234,7 +1248,10 @@ static int gemm_entry(const void* x, const void* w, const float* bias, void* out
     p.stages = stages;   // 0: the default of the mode
     p.wait_cycles = g_wait_cycles;
     p.withhold = g_withhold;
-    p.tile_group = nullptr; p.group_rows = 0; p.act_kind = 0; p.act_limit = 0.f; p.act_alpha = 1.f;
+    // gated: 0 no; 1 + the activation's kind otherwise (1: silu, 3: gelu in its tanh form, which the kernels for many
+    // tokens apply; the few-token kernels know silu only)
+    p.tile_group = nullptr; p.group_rows = 0; p.act_kind = gated > 1 ? gated - 1 : 0; p.act_limit = 0.f; p.act_alpha = 1.f;
+    if (gated > 1 && (swap || gated != 3)) return RB_ERR_BAD_SIZE;
     CUtensorMap ma, mb;
     int rc;
     if (swap) {

@@ -668,14 +668,17 @@ def set_wait_limit(cycles: int = 0, withhold_first_stage: bool = False) -> None:
 @_profiled(lambda a, facts: (_cost.gated_linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, _esz(a["out"])) if a["gated"] else
                          _cost.linear(_rows(a), a["w"].shape[0], a["w"].shape[1], 2, 2, _esz(a["out"]), _n_in(a["out"]))))
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                 m: Optional[int] = None, stages: int = 0, gated: bool = False) -> bool:
+                 m: Optional[int] = None, stages: int = 0, gated: bool = False, act: str = "silu") -> bool:
     """out = x . w^T on the tensor cores; x, w bfloat16, out bfloat16 [M, N] or float32 [M, N] or
     float32 [S, M, N] (S partial sums over K, to be added by the consumer).  Returns False when the
     kernel refuses the layout (K or a row stride not a multiple of 8, a pointer off 16 bytes);
     the caller then uses the plain kernel.
 
     ``gated``: w's rows alternate in blocks of 16 between a gate and an up projection of the same
-    16 outputs, and out is bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue."""
+    16 outputs, and out is bfloat16 [M, N / 2] = act(gate) * up, computed in the epilogue (``act`` "silu", or
+    "gelu_tanh" for more than 128 rows)."""
+    if gated and act not in ("silu", "gelu_tanh"):
+        raise KernelError(f"gemm_tcgen05: activation {act!r} is not built into the product")
     M = x.shape[0] if m is None else m
     N, K = w.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous() \
@@ -692,7 +695,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError("gemm_tcgen05: bias must be float32 [N]")
     rc = _lib().rb_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
-                                ldo, splits, split_stride, stages, 1 if gated else 0, _ptr(status_word(x.device)), _stream())
+                                ldo, splits, split_stride, stages, (1 + GATED_ACTS[act]) if gated else 0,
+                                _ptr(status_word(x.device)), _stream())
     if rc == 10003:
         return False
     _check(rc, "gemm_tcgen05")

@@ -116,10 +116,11 @@ class Linear:
         return True
 
     @_labelled
-    def forward_gated(self, x: torch.Tensor, m: int) -> torch.Tensor:
-        """[M, N / 2] = silu(gate(x)) * up(x) in one kernel (needs ``interleave_pairs``)."""
+    def forward_gated(self, x: torch.Tensor, m: int, act: str = "silu") -> torch.Tensor:
+        """[M, N / 2] = act(gate(x)) * up(x) in one kernel (needs ``interleave_pairs``; "gelu_tanh" needs more than
+        128 rows)."""
         out = torch.empty((m, self.n // 2), dtype=torch.bfloat16, device=x.device)
-        if not kernels.gemm_tcgen05(x, self.weight, out, self.bias, m, gated=True):
+        if not kernels.gemm_tcgen05(x, self.weight, out, self.bias, m, gated=True, act=act):
             raise KernelError("the gated matrix product refused a layout that interleave_pairs accepted")
         return out
 

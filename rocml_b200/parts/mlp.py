@@ -22,8 +22,8 @@ class GatedMLP(FeedForward):
     """gate and up are one stacked product [T, 2I]; act(gate) * up -> [T, I]; down -> [T, H].
     The activation is a parameter: 'silu' (g / (1 + exp(-g)), rocml-kernels/kernels/
     silu_mul.hip:15-18), which the products apply in their epilogues, or 'gelu_tanh'
-    (g / 2 * (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))), applied by a kernel of its own on the
-    product's result (32-bit partial sums for few tokens)."""
+    (g / 2 * (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))), which the products for more than 128 tokens apply
+    in their epilogues and a kernel of its own applies otherwise (on 32-bit partial sums for few tokens)."""
 
     graph_safe = True
 
@@ -49,8 +49,8 @@ class GatedMLP(FeedForward):
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str) -> None:
         self.gate_up.load(tensors, prefix)
         self.down.load(tensors, prefix)
-        if self.env.act_dtype == torch.bfloat16 and self.act == "silu":
-            self.gate_up.interleave_pairs()     # silu(gate) * up then happens inside the product
+        if self.env.act_dtype == torch.bfloat16:
+            self.gate_up.interleave_pairs()     # act(gate) * up then happens inside the product
 
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
@@ -72,7 +72,7 @@ class GatedMLP(FeedForward):
         """Whether forward() can be handed a DeferredNorm for this step: only the product of two blocks
         that applies the activation itself also applies the rows' 1/RMS."""
         T = batch.n_tokens
-        return (self.gate_up.paired and T <= GATED_PAIR_MAX_ROWS and self.gate_up.weight.dtype == torch.bfloat16
+        return (self.act == "silu" and self.gate_up.paired and T <= GATED_PAIR_MAX_ROWS and self.gate_up.weight.dtype == torch.bfloat16
                 and self.gate_up._splits(T) == 2 and self.gate_up.k > 64)
 
     can_add_into = True    # forward() accepts add_into=residual (see parts.base)
@@ -87,8 +87,8 @@ class GatedMLP(FeedForward):
                 xn = xn.materialize()     # the kernel declined after all: the norm's own kernel, then as always
         if h is None and self.gate_up.paired and T > 128:
             # many tokens: the activation happens in the product's epilogue, hidden behind the next tile
-            h = self.gate_up.forward_gated(xn, T)
-        elif h is None and self.gate_up.paired:
+            h = self.gate_up.forward_gated(xn, T, self.act)
+        elif h is None and self.gate_up.paired and self.act == "silu":
             # few tokens, the sum over K in two halves: the activation happens where the halves meet
             h = self.gate_up.forward_gated_pair(xn, T)
         if h is None:
