@@ -765,3 +765,99 @@ def test_trace_replay_and_command_line(models, tmp_path):
     r = subprocess.run([sys.executable, "-m", "rocml_b200", "generate", "--model", f.folder, "--prompt-ids", "1,2,3", "-n", "5"],
                        capture_output=True, text=True, timeout=600, cwd=root)
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+# ---- configurations drawn at random -----------------------------------------------------------------------------
+
+def random_configuration(seed):
+    """A Zokelorn configuration whose every size, option and constant is drawn from a seed (sizes stay small)."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([48, 64, 72, 96, 128, 160, 256])
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        kind = r.choice(["attention", "lightning", "retention"])
+        if kind == "attention":
+            heads = r.choice([1, 2, 3, 4, 6, 8, 12])
+            kv = r.choice([g for g in (1, 2, 3, 4, 6, 8, 12) if heads % g == 0])
+            dim = r.choice([8, 16, 24, 32, 40, 64, 96, 128])
+            rot = {"base": r.choice([100.0, 10000.0, 1e6]), "dims": r.choice([0, 2, dim // 2 // 2 * 2, dim])}
+            if r.random() < 0.6:
+                low = r.choice([0.5, 1.0, 2.0])
+                rot["scaling"] = {"factor": r.choice([2.0, 8.0, 32.0]), "low": low, "high": low * r.choice([2.0, 4.0]),
+                                  "original": r.choice([16, 64, 1024, 8192])}
+            mixer = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": r.choice([8, 16, 24, 32, 40, 64, 96, 128]),
+                     "scale": r.uniform(0.05, 0.4), "mask": {"size": r.choice([1, 2, 7, 31, 64, 65, 100, 128, 200, 1000])}, "rot": rot}
+        else:
+            heads = r.randint(1, 6)
+            mixer = {"heads": heads, "dim": r.choice([4, 8, 16, 20, 32, 64, 72, 128, 136]), "vdim": r.choice([4, 8, 12, 32, 64, 96, 128, 160]),
+                     "decay": [r.choice([0.0, 1.0, r.uniform(0.3, 0.9), 1.0 - 2.0 ** -r.randint(3, 10)]) for _ in range(heads)]}
+        u = r.random()
+        if u < 0.1:
+            mlp = None
+        elif u < 0.5:
+            mlp = {"kind": "dense", "ff": 4 * r.randint(2, 50)}
+        else:
+            experts = r.choice([1, 2, 4, 6, 8, 12, 16, 24])
+            groups = r.choice([g for g in (1, 2, 3, 4, 6, 8) if experts % g == 0])
+            keep = r.randint(1, groups)
+            top = r.randint(1, min(6, keep * (experts // groups)))
+            router = {"experts": experts, "top": top}
+            if groups > 1 or r.random() < 0.3:
+                router["groups"] = {"count": groups, "keep": keep}
+            mlp = {"kind": "moe", "expert": {"ff": 4 * r.randint(1, 16)}, "router": router}
+            if r.random() < 0.6:
+                mlp["shared"] = {"ff": 4 * r.randint(1, 24)}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    cfg = {"architecture": "Zokelorn", "vocab": r.randint(40, 700), "width": width, "norm": {"eps": r.choice([1e-6, 1e-5, 1e-4])},
+           "layers": layers}
+    if r.random() < 0.6:
+        a = r.randint(0, len(layers) - 1)
+        cfg["loop"] = {"start": a, "stop": r.randint(a + 1, len(layers)), "times": r.randint(1, 3)}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Ten configurations whose sizes, options and constants come from a seed: in 32-bit a whole prompt, the same prompt
+    as a first piece and single tokens, and two unequal requests side by side, against the plain implementation; in
+    bfloat16 the whole prompt, loosely (it must run and stay near)."""
+    from rocml_b200 import StepEntry
+    cfg = random_configuration(seed)
+    folder = str(tmp_path / "m")
+    write_zokelorn(folder, cfg, seed=seed, std=0.06, sharp=2.0)
+    plain = Folder(folder)
+    n = 150
+    ids = prompt(seed, n, cfg["vocab"])
+    other = prompt(seed + 100, 70, cfg["vocab"])
+    want, calls = plain(ids), plain.calls(ids)
+    eng = engine(folder, "float32")
+    slot = eng.new_sequence()
+    got = eng.step([StepEntry(slot, ids, list(range(n)))])
+    eng.release(slot)
+    assert_rows(got, want, calls, "float32", f"seed {seed} whole")
+    a, b = eng.new_sequence(), eng.new_sequence()
+    out = eng.step([StepEntry(a, ids[:97], [96]), StepEntry(b, other[:66], list(range(66)))])
+    rows_a, rows_b = [out[:1].clone()], [out[1:].clone()]
+    for t in range(97, n):
+        entries = [StepEntry(a, [ids[t]], [0])] + ([StepEntry(b, [other[t - 97 + 66]], [0])] if t - 97 + 66 < 70 else [])
+        out = eng.step(entries)
+        rows_a.append(out[:1].clone())
+        if len(entries) > 1:
+            rows_b.append(out[1:2].clone())
+        elif t - 97 + 66 == 70:
+            eng.release(b)
+    eng.release(a)
+    assert_rows(torch.cat(rows_a), want[96:], calls, "float32", f"seed {seed} decoded", first_row=96)
+    assert_rows(torch.cat(rows_b), plain(other), plain.calls(other), "float32", f"seed {seed} second request")
+    eng.cache.check_invariants()
+    eng = engine(folder, "bfloat16")
+    slot = eng.new_sequence()
+    got = eng.step([StepEntry(slot, ids, list(range(n)))]).double().cpu()
+    eng.release(slot)
+    assert bool(torch.isfinite(got).all())
+    near = torch.nonzero(calls < CLOSE["bfloat16"])[:, 0]
+    upto = n if not len(near) else int(near[0])
+    if upto >= 20:
+        err = (got[:upto] - want[:upto]).abs().amax(-1) / want[:upto].abs().amax(-1)
+        assert float(err.median()) < TOL["bfloat16"], f"seed {seed} bfloat16: median {float(err.median()):.3g}"
